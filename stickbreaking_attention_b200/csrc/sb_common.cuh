@@ -1,0 +1,130 @@
+// Shared host/device definitions of the stick-breaking attention library: workspace layout, the work-item
+// table that every kernel walks, and small device helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "../../include/sbattn.h"
+
+namespace sb {
+
+constexpr int kTileQ = 128;    // query rows per work item
+constexpr int kTileKV = 64;    // keys per carry slot: carries are kept at every 64-key boundary
+constexpr int kMaxHeadDim = 128;
+
+// One sequence of the pack (or one batch entry of the batched layout).
+struct SeqInfo {
+    int32_t batch;      // index along B (0 for the packed layout)
+    int32_t start;      // first token along T
+    int32_t len;        // tokens
+    int32_t slot_base;  // first carry slot of this sequence (per head)
+};
+
+// Start of the forward workspace.  The prep kernel fills it; all later kernels only read it.
+struct WsHeader {
+    int32_t n_items;      // work items per head = sum over sequences of ceil(len/128)
+    int32_t n_seqs;
+    int32_t total_slots;  // carry slots per head actually used
+    int32_t bad;          // non-zero: sequence table rejected, n_items is 0
+    int32_t pad[60];
+};
+static_assert(sizeof(WsHeader) == 256, "header is one 256-byte line");
+
+// Host-side description of where things live inside the workspaces (all offsets in bytes).
+struct WsLayout {
+    int32_t n_seqs;      // sequences (packed: num_seqs, batched: B)
+    int32_t n_max;       // max 128-row tiles of one sequence
+    int32_t max_items;   // upper bound on items per head
+    int64_t slot_cap;    // upper bound on carry slots per head
+    int32_t hb;          // heads (batched: heads; the batch index comes from the sequence)
+    size_t off_seqs, off_items, off_bins, off_carry;
+    size_t fwd_bytes;    // with carries if save_carries
+    size_t bwd_bytes;
+};
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+inline WsLayout make_layout(const SbParams& p) {
+    WsLayout L{};
+    const bool batched = p.batch > 0;
+    L.n_seqs = batched ? p.batch : p.num_seqs;
+    const int64_t maxlen = batched ? p.tokens : (p.max_seqlen > 0 ? (p.max_seqlen < p.tokens ? p.max_seqlen : p.tokens) : p.tokens);
+    L.n_max = (int32_t)((maxlen + kTileQ - 1) / kTileQ);
+    if (L.n_max < 1) L.n_max = 1;
+    if (batched) {
+        L.max_items = L.n_seqs * L.n_max;
+        L.slot_cap = (int64_t)L.n_seqs * L.n_max * (L.n_max + 1);
+    } else {
+        // sum ceil(len/128) <= T/128 + S ; sum n(n+1) <= (n_max+1) * sum n
+        const int64_t items = p.tokens / kTileQ + L.n_seqs;
+        L.max_items = (int32_t)items;
+        L.slot_cap = items * (L.n_max + 1);
+    }
+    L.hb = p.heads;
+    size_t off = sizeof(WsHeader);
+    L.off_seqs = off;
+    off = align_up(off + sizeof(SeqInfo) * (size_t)L.n_seqs, 256);
+    L.off_items = off;
+    off = align_up(off + sizeof(int2) * (size_t)L.max_items, 256);
+    L.off_bins = off;
+    off = align_up(off + sizeof(int32_t) * (size_t)(2 * (L.n_max + 2)), 256);
+    L.off_carry = off;
+    const size_t carry = sizeof(float) * (size_t)L.hb * (size_t)L.slot_cap * kTileQ;
+    L.fwd_bytes = off + (p.save_carries ? carry : 0);
+    L.bwd_bytes = align_up(carry, 256);
+    return L;
+}
+
+// What the kernels need of a [B,H,T,D] tensor.
+struct MatView {
+    char* ptr;
+    int64_t sb, sh, st;  // element strides
+};
+struct VecView {
+    char* ptr;
+    int64_t sb, sh, st;
+};
+inline MatView view(const SbMat& m) { return MatView{(char*)m.ptr, m.stride_b, m.stride_h, m.stride_t}; }
+inline VecView view(const SbVec& m) { return VecView{(char*)m.ptr, m.stride_b, m.stride_h, m.stride_t}; }
+
+// Arguments common to every attention kernel.
+struct KArgs {
+    const WsHeader* hdr;
+    const SeqInfo* seqs;
+    const int2* items;      // (sequence, 128-row tile), heaviest first
+    float* carry_w;         // forward carries  [heads][slot_cap][128], may be null in a no-grad forward
+    float* carry_c;         // backward carries [heads][slot_cap][128]
+    int64_t slot_cap;
+    int32_t heads, head_dim, attend_current;
+    float inv_temp;
+    MatView q, k, v, o, d_o, dq, dk, dv;
+    VecView rem, nla, d_rem;
+    uint32_t* status;
+};
+
+// carry slot of (128-row tile qt of a sequence, 64-key tile kh): kh in [0, 2*qt+1]
+__host__ __device__ inline int64_t carry_slot(int32_t slot_base, int32_t qt, int32_t kh) {
+    return (int64_t)slot_base + (int64_t)qt * (qt + 1) + kh;
+}
+
+template <typename T> __device__ inline float to_f32(T x);
+template <> __device__ inline float to_f32<float>(float x) { return x; }
+template <> __device__ inline float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ inline float to_f32<__half>(__half x) { return __half2float(x); }
+template <typename T> __device__ inline T from_f32(float x);
+template <> __device__ inline float from_f32<float>(float x) { return x; }
+template <> __device__ inline __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ inline __half from_f32<__half>(float x) { return __float2half_rn(x); }
+
+// launchers implemented in the .cu files (each returns a cudaError_t as int)
+int launch_prep(const SbParams& p, const WsLayout& L, cudaStream_t st);
+int launch_simt_fwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
+int launch_simt_bwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
+bool tensor_path_eligible(const SbParams& p, bool backward, int* why);
+int launch_tensor_fwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
+int launch_tensor_bwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
+
+}  // namespace sb

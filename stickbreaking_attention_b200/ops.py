@@ -1,0 +1,222 @@
+"""Host launchers with the reference's names and argument meaning, on top of the C ABI.
+
+``varlen_fwd`` / ``varlen_bwd`` mirror stickbreaking_attention/sb_varlen/sb_varlen_fwd.py:411 and
+sb_varlen_bwd.py:483; ``attn_fwd`` / ``attn_bwd`` mirror sb_attn/sb_fwd.py:137 (``_fwd``) and sb_bwd.py:162
+(``_bwd``).  Differences that a caller can see: the forward returns one more value, an opaque workspace that
+the backward needs (the tile table and the per-tile carries), and gradients of the batched layout keep the input
+dtype instead of being forced to bfloat16 (sb_bwd.py:172-173).
+"""
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+from ._lib import SbMat, SbParams, SbVec
+
+_DTYPES = {torch.bfloat16: _lib.SBATTN_BF16, torch.float32: _lib.SBATTN_F32, torch.float16: _lib.SBATTN_F16}
+_PATHS = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tensor": _lib.PATH_TENSOR}
+_status_words = {}
+_forced_path = os.environ.get("SBATTN_PATH", "auto")
+
+
+def set_path(name):
+    """'auto' (default), 'simt' (fp32-arithmetic kernels) or 'tensor' (tcgen05 kernels or an error)."""
+    global _forced_path
+    if name not in _PATHS:
+        raise ValueError(name)
+    _forced_path = name
+
+
+def get_path():
+    return _forced_path
+
+
+def status_word(device):
+    """int32 device word the kernels OR their SBATTN_ST_* bits into (one per device, never reset by the library)."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _status_words[key]
+
+
+def check_status(device=None, reset=True):
+    """Synchronises and raises if a kernel reported bad sequence ends or a wait that ran out."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = status_word(device)
+    val = int(w.item())
+    if reset:
+        w.zero_()
+    if val & _lib.ST_BAD_SEQLENS:
+        raise ValueError("cu_seqlens rejected on the device: ends must be non-decreasing, at most the number of "
+                         "tokens, and no sequence longer than max_seqlens")
+    if val & _lib.ST_TIMEOUT:
+        raise RuntimeError("a stick-breaking attention kernel gave up waiting (results are invalid)")
+    return val
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("stick-breaking attention runs on CUDA tensors only (there is no CPU implementation)")
+
+
+def _mat(t, batched):
+    if t is None:
+        return SbMat(None, 0, 0, 0)
+    if batched:
+        return SbMat(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+    return SbMat(t.data_ptr(), 0, t.stride(0), t.stride(1))
+
+
+def _vec(t, batched):
+    if t is None:
+        return SbVec(None, 0, 0, 0)
+    if batched:
+        return SbVec(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+    return SbVec(t.data_ptr(), 0, t.stride(0), t.stride(1))
+
+
+def _unit_inner(t):
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def _empty_like_rows(t):
+    out = torch.empty_like(t)
+    return out if out.stride(-1) == 1 else torch.empty(t.shape, dtype=t.dtype, device=t.device)
+
+
+def _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, save_carries):
+    if q.dtype not in _DTYPES:
+        raise TypeError(f"unsupported dtype {q.dtype}")
+    p = SbParams()
+    p.dtype = _DTYPES[q.dtype]
+    p.path = _PATHS[_forced_path]
+    if batched:
+        B, H, T, D = q.shape
+        p.batch, p.num_seqs, p.cu_width, p.cu_seqlens, p.max_seqlen = B, 0, 4, None, T
+    else:
+        H, T, D = q.shape
+        p.batch = 0
+        p.num_seqs = cu_seqlens.numel()
+        p.cu_width = cu_seqlens.element_size()
+        p.cu_seqlens = cu_seqlens.data_ptr()
+        p.max_seqlen = int(max_seqlens)
+    p.heads, p.tokens, p.head_dim = H, T, D
+    p.attend_current = int(bool(attend_current))
+    p.inv_temp = float(logit_scale)
+    p.save_carries = int(bool(save_carries))
+    p.status = status_word(q.device).data_ptr()
+    p.stream = torch.cuda.current_stream(q.device).cuda_stream
+    return p
+
+
+def _workspace_sizes(p):
+    fb, bb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    _lib.check(_lib.lib().sbattn_workspace_bytes(ctypes.byref(p), ctypes.byref(fb), ctypes.byref(bb)),
+               "sbattn_workspace_bytes")
+    return fb.value, bb.value
+
+
+def _check_qkv(q, k, v, ndim):
+    if q.dim() != ndim or k.shape != q.shape or v.shape != q.shape:
+        raise ValueError(f"q, k, v must share one {ndim}-d shape, got {tuple(q.shape)} {tuple(k.shape)} {tuple(v.shape)}")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("q, k, v must share one dtype")
+    if k.device != q.device or v.device != q.device:
+        raise ValueError("q, k, v must live on one device")
+    if q.size(-1) > 128:
+        raise ValueError("head_dim above 128 is not supported")
+
+
+def _prep_cu(cu_seqlens, q, max_seqlens):
+    if cu_seqlens.dtype not in (torch.int32, torch.int64):
+        raise TypeError("cu_seqlens must be int32 or int64")
+    if cu_seqlens.dim() != 1:
+        raise ValueError("cu_seqlens must be 1-d")
+    if cu_seqlens.device != q.device:
+        cu_seqlens = cu_seqlens.to(q.device)
+    cu_seqlens = cu_seqlens.contiguous()
+    if max_seqlens is None:
+        # one device-to-host read, exactly what callers of the reference do to obtain this argument
+        if cu_seqlens.numel() == 0:
+            max_seqlens = 0
+        else:
+            lens = torch.diff(cu_seqlens, prepend=cu_seqlens.new_zeros(1))
+            max_seqlens = int(lens.max().item())
+    return cu_seqlens, int(max_seqlens)
+
+
+def _forward(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad):
+    _require_cuda(q, k, v)
+    q, k, v = _unit_inner(q), _unit_inner(k), _unit_inner(v)
+    with torch.cuda.device(q.device):
+        o = _empty_like_rows(q)
+        rem = torch.zeros(q.shape[:-1], dtype=q.dtype, device=q.device)
+        neg_log_acc = torch.zeros(q.shape[:-1], dtype=torch.float32, device=q.device)
+        p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, not no_grad)
+        fwd_bytes, _ = _workspace_sizes(p)
+        ws = torch.empty(fwd_bytes, dtype=torch.uint8, device=q.device)
+        p.q, p.k, p.v, p.o = _mat(q, batched), _mat(k, batched), _mat(v, batched), _mat(o, batched)
+        p.rem, p.neg_log_acc = _vec(rem, batched), _vec(neg_log_acc, batched)
+        p.fwd_workspace, p.fwd_workspace_bytes = ws.data_ptr(), fwd_bytes
+        _lib.check(_lib.lib().sbattn_fwd(ctypes.byref(p)), "sbattn_fwd")
+        if os.environ.get("SBATTN_CHECK_STATUS") == "1":
+            check_status(q.device)
+    return o, rem, neg_log_acc, ws
+
+
+def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current):
+    _require_cuda(q, k, v, do, dr, ws)
+    q, k, v, do = _unit_inner(q), _unit_inner(k), _unit_inner(v), _unit_inner(do)
+    if do.dtype != q.dtype:
+        do = do.to(q.dtype)
+    if dr.dtype != q.dtype:
+        dr = dr.to(q.dtype)
+    with torch.cuda.device(q.device):
+        dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+        if dq.stride(-1) != 1:
+            dq, dk, dv = (torch.zeros(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
+        p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, True)
+        fwd_bytes, bwd_bytes = _workspace_sizes(p)
+        if ws.numel() < fwd_bytes:
+            raise ValueError("the forward workspace does not belong to this problem (was the forward run with no_grad?)")
+        bws = torch.empty(bwd_bytes, dtype=torch.uint8, device=q.device)
+        p.q, p.k, p.v = _mat(q, batched), _mat(k, batched), _mat(v, batched)
+        p.d_o, p.d_rem = _mat(do, batched), _vec(dr, batched)
+        p.dq, p.dk, p.dv = _mat(dq, batched), _mat(dk, batched), _mat(dv, batched)
+        p.fwd_workspace, p.fwd_workspace_bytes = ws.data_ptr(), ws.numel()
+        p.bwd_workspace, p.bwd_workspace_bytes = bws.data_ptr(), bwd_bytes
+        _lib.check(_lib.lib().sbattn_bwd(ctypes.byref(p)), "sbattn_bwd")
+        if os.environ.get("SBATTN_CHECK_STATUS") == "1":
+            check_status(q.device)
+    return dq, dk, dv
+
+
+def varlen_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=False, no_grad=False):
+    """Packed layout: q, k, v [H, T, D]; cu_seqlens = cumulative sequence ends without a leading zero.
+
+    Returns (o, rem, neg_log_acc, workspace).  Mirrors varlen_fwd of the reference (sb_varlen_fwd.py:411-452)."""
+    _check_qkv(q, k, v, 3)
+    cu_seqlens, max_seqlens = _prep_cu(cu_seqlens, q, max_seqlens)
+    return _forward(q, k, v, False, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad)
+
+
+def varlen_bwd(do, dr, q, k, v, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current=False):
+    """Returns (dq, dk, dv).  Mirrors varlen_bwd of the reference (sb_varlen_bwd.py:483-539); ``workspace`` takes
+    the place of its ``neg_log_acc`` argument."""
+    _check_qkv(q, k, v, 3)
+    cu_seqlens, max_seqlens = _prep_cu(cu_seqlens, q, max_seqlens)
+    return _backward(do, dr, q, k, v, False, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current)
+
+
+def attn_fwd(q, k, v, logit_scale, attend_current=False, no_grad=False):
+    """Batched layout: q, k, v [B, H, T, D].  Mirrors _fwd of the reference (sb_attn/sb_fwd.py:137-173)."""
+    _check_qkv(q, k, v, 4)
+    return _forward(q, k, v, True, None, q.size(2), logit_scale, attend_current, no_grad)
+
+
+def attn_bwd(do, dr, q, k, v, workspace, logit_scale, attend_current=False):
+    """Mirrors _bwd of the reference (sb_attn/sb_bwd.py:162-204)."""
+    _check_qkv(q, k, v, 4)
+    return _backward(do, dr, q, k, v, True, None, q.size(2), workspace, logit_scale, attend_current)

@@ -1,0 +1,182 @@
+"""GPU parity: the CUDA path (through the public Python API, hence the C ABI) against the reference fixtures and the
+numpy oracle on the same seeded inputs."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from cases import CASES, inv_temp_of, make_inputs
+from util import (TOL_BF16, TOL_F32, assert_close, oracle_varlen, rounded, run_batched, run_varlen, synth)
+from oracle import sb_oracle as orc
+
+pytestmark = pytest.mark.gpu
+NAMES = ("o", "rem", "dq", "dk", "dv")
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def gold(name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    return [z[k].astype(np.float64) for k in NAMES]
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_fixture_float32_mode(name):
+    """float32 inputs: max-abs <= 1e-5 against the reference's own outputs."""
+    spec = CASES[name]
+    ins = make_inputs(spec)
+    got = run_varlen(*ins, spec["lengths"], inv_temp_of(spec), spec["attend_current"], torch.float32)
+    assert_close(NAMES, got, gold(name), TOL_F32, name)
+
+
+@pytest.mark.parametrize("name", sorted(n for n in CASES if CASES[n]["bf16"]))
+@pytest.mark.parametrize("path", ["auto", "simt"])
+def test_fixture_bf16(name, path):
+    """bf16 inputs (the fixtures of these cases were produced from bf16-representable values): max-abs <= 2e-2."""
+    import stickbreaking_attention_b200 as sb
+    spec = CASES[name]
+    ins = make_inputs(spec)
+    sb.set_path(path)
+    try:
+        got = run_varlen(*ins, spec["lengths"], inv_temp_of(spec), spec["attend_current"], torch.bfloat16)
+    finally:
+        sb.set_path("auto")
+    assert_close(NAMES, got, gold(name), TOL_BF16, name)
+
+
+@pytest.mark.parametrize("zero_start,cu_dtype", [(False, torch.int64), (True, torch.int32), (False, torch.int32)])
+def test_cu_seqlens_conventions(zero_start, cu_dtype):
+    spec = CASES["tiny_edges"]
+    ins = make_inputs(spec)
+    got = run_varlen(*ins, spec["lengths"], inv_temp_of(spec), False, torch.float32, zero_start=zero_start,
+                     cu_dtype=cu_dtype, max_seqlens=None if zero_start else "given")
+    assert_close(NAMES, got, gold("tiny_edges"), TOL_F32)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, TOL_BF16), (torch.float16, TOL_BF16), (torch.float32, TOL_F32)])
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("attend_current", [False, True])
+def test_ragged_pack_against_oracle(dtype, tol, D, attend_current):
+    lengths = [1, 127, 128, 129, 300, 2, 64, 513, 255]
+    H, T = 3, sum(lengths)
+    ins = [rounded(x, dtype) for x in synth(H, T, D, seed=5)]
+    it = 1 / math.sqrt(D)
+    got = run_varlen(*ins, lengths, it, attend_current, dtype)
+    want = oracle_varlen(*ins, lengths, it, attend_current)
+    assert_close(NAMES, got, want, tol, f"D={D}")
+
+
+@pytest.mark.parametrize("B,H,T,D", [(2, 3, 500, 50), (1, 2, 256, 16), (2, 1, 512, 32), (2, 2, 640, 64),
+                                     (1, 3, 1024, 128)])
+@pytest.mark.parametrize("attend_current", [False, True])
+def test_batched_reference_distribution(B, H, T, D, attend_current):
+    """Shapes and input distribution of the reference's tests/test_attn.py:40-59 (including head_dim 50, T 500)."""
+    ins = synth(B * H, T, D, seed=1337, dist="reftest")
+    ins = [rounded(x, torch.bfloat16) for x in ins]
+    ins4 = [x.reshape((B, H) + x.shape[1:]) for x in ins]
+    it = 1 / math.sqrt(D)
+    got = run_batched(*ins4, it, attend_current, torch.bfloat16)
+    want = orc.sb_batched_fwd_bwd(*ins4, it, attend_current)
+    assert_close(NAMES, got, want, TOL_BF16, f"{B,H,T,D}")
+
+
+def test_reference_test_quantity_single_sequence():
+    """What the reference's tests/test_varlen.py:97-112 checks: o + rem*v and its gradients, eps 0.05 there."""
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    H, T, D = 3, 4096, 128
+    q, k, v, do, _ = [rounded(x, torch.bfloat16) for x in synth(H, T, D, seed=1337, dist="reftest")]
+    tq, tk, tv = (torch.from_numpy(x).cuda().bfloat16().requires_grad_() for x in (q, k, v))
+    tdo = torch.from_numpy(do).cuda().bfloat16()
+    cu = torch.tensor([T], device="cuda", dtype=torch.int64)
+    o, rem = sb_attn_varlen(tq, tk, tv, cu, T, inv_temp=1 / math.sqrt(D), zero_start=False)
+    out = o + rem[..., None] * tv
+    dq, dk, dv = torch.autograd.grad(out, (tq, tk, tv), tdo)
+    drem = (do * v).sum(-1)
+    ro, rrem, rdq, rdk, rdv = orc.sb_varlen_fwd_bwd(q, k, v, do, drem, [T], 1 / math.sqrt(D))
+    rout = ro + rrem[..., None] * v
+    rdv = rdv + rrem[..., None] * do
+    for n, g, w in zip(("out", "dq", "dk", "dv"), (out, dq, dk, dv), (rout, rdq, rdk, rdv)):
+        err = np.abs(g.detach().double().cpu().numpy() - w).max()
+        assert err < TOL_BF16 * 1.5, (n, err)
+
+
+def test_strided_inputs_token_major():
+    """The reference's benchmark passes [T,H,D] tensors permuted to [H,T,D] (benchmarks/varlen.py:44-46)."""
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    lengths = [200, 312]
+    H, T, D = 4, 512, 64
+    q, k, v, do, drem = [rounded(x, torch.bfloat16) for x in synth(H, T, D, seed=9)]
+    dev = lambda x: torch.from_numpy(np.ascontiguousarray(x.transpose(1, 0, 2))).cuda().bfloat16()
+    tq, tk, tv = (dev(x).requires_grad_() for x in (q, k, v))
+    cu = torch.tensor(np.cumsum(lengths), device="cuda")
+    o, rem = sb_attn_varlen(tq.permute(1, 0, 2), tk.permute(1, 0, 2), tv.permute(1, 0, 2), cu, max(lengths),
+                            zero_start=False)
+    tdo = torch.from_numpy(do).cuda().bfloat16()
+    tdr = torch.from_numpy(drem).cuda().bfloat16()
+    dq, dk, dv = torch.autograd.grad([o, rem], [tq, tk, tv], [tdo, tdr])
+    got = [o, rem] + [x.permute(1, 0, 2) for x in (dq, dk, dv)]
+    got = [x.detach().double().cpu().numpy() for x in got]
+    want = oracle_varlen(q, k, v, do, drem, lengths, 1 / math.sqrt(D), False)
+    assert_close(NAMES, got, want, TOL_BF16)
+
+
+def test_rows_sum_to_one_and_linearity_full_size():
+    """Size-independent properties on the 16384-token benchmark pack: with v = 1 every o entry equals 1 - rem,
+    and o is linear in v."""
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    lengths = [2943, 3503, 2192, 1807, 3696, 649, 1594]
+    H, T, D = 4, sum(lengths), 128
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(H, T, D, generator=g).cuda().bfloat16()
+    k = torch.randn(H, T, D, generator=g).cuda().bfloat16()
+    v1 = torch.randn(H, T, D, generator=g).cuda().bfloat16()
+    cu = torch.tensor(np.cumsum(lengths), device="cuda")
+    ones = torch.ones_like(v1)
+    o_ones, rem = sb_attn_varlen(q, k, ones, cu, max(lengths), zero_start=False)
+    assert (o_ones.float() - (1 - rem.float())[..., None]).abs().max() < 2e-2
+    o1, rem1 = sb_attn_varlen(q, k, v1, cu, max(lengths), zero_start=False)
+    o2, _ = sb_attn_varlen(q, k, v1 * 2, cu, max(lengths), zero_start=False)
+    assert torch.equal(rem, rem1)
+    assert (o2.float() - 2 * o1.float()).abs().max() < 4e-2
+    # first row of every sequence attends nothing
+    starts = [0] + list(np.cumsum(lengths)[:-1])
+    assert torch.all(o1[:, starts] == 0) and torch.all(rem1[:, starts] == 1)
+
+
+def test_bitwise_deterministic():
+    lengths = [700, 324]
+    H, T, D = 2, 1024, 128
+    ins = [rounded(x, torch.bfloat16) for x in synth(H, T, D, seed=21)]
+    a = run_varlen(*ins, lengths, 0.1, False, torch.bfloat16)
+    b = run_varlen(*ins, lengths, 0.1, False, torch.bfloat16)
+    for x, y in zip(a, b):
+        assert np.array_equal(x, y)
+
+
+def test_bad_seqlens_reported_not_faulting():
+    import stickbreaking_attention_b200 as sb
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    H, T, D = 1, 256, 64
+    q = torch.randn(H, T, D, device="cuda", dtype=torch.bfloat16)
+    sb.check_status()
+    cu = torch.tensor([200, 100], device="cuda")  # decreasing
+    sb_attn_varlen(q, q, q, cu, 256, zero_start=False)
+    with pytest.raises(ValueError):
+        sb.check_status()
+    cu = torch.tensor([100, 300], device="cuda")  # beyond T
+    sb_attn_varlen(q, q, q, cu, 256, zero_start=False)
+    with pytest.raises(ValueError):
+        sb.check_status()
+    assert sb.check_status() == 0
+
+
+def test_empty_and_no_grad():
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    q = torch.randn(2, 0, 64, device="cuda", dtype=torch.bfloat16)
+    o, rem = sb_attn_varlen(q, q, q, torch.zeros(0, device="cuda", dtype=torch.int64), 0, zero_start=False)
+    assert o.shape == (2, 0, 64) and rem.shape == (2, 0)
+    q = torch.randn(2, 130, 64, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        o, rem = sb_attn_varlen(q, q, q, torch.tensor([0, 130], device="cuda"), 130)
+    assert torch.isfinite(o.float()).all()

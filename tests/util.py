@@ -1,0 +1,72 @@
+"""Helpers shared by the GPU parity tests: run the CUDA path through the public API and the oracle on the same data."""
+import numpy as np
+import torch
+
+from oracle import sb_oracle as orc
+
+TOL_BF16 = 2e-2   # max-abs bar for bf16 inputs against an fp32/fp64 reference of the same (rounded) inputs
+TOL_F32 = 1e-5    # max-abs bar in the float32-input mode
+
+
+def to_dev(x, dtype, device="cuda"):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(device=device, dtype=dtype)
+
+
+def run_varlen(q, k, v, do, drem, lengths, inv_temp, attend_current, dtype, zero_start=False, cu_dtype=torch.int64,
+               max_seqlens="given"):
+    """numpy in, numpy (float64) out: o, rem, dq, dk, dv from sb_attn_varlen + autograd."""
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    tq, tk, tv = (to_dev(x, dtype).requires_grad_() for x in (q, k, v))
+    tdo, tdr = to_dev(do, dtype), to_dev(drem, dtype)
+    ends = np.cumsum(np.asarray(lengths, dtype=np.int64))
+    cu = np.concatenate([[0], ends]) if zero_start else ends
+    cu = torch.from_numpy(cu).to(device="cuda", dtype=cu_dtype)
+    ms = int(max(lengths)) if max_seqlens == "given" else max_seqlens
+    o, rem = sb_attn_varlen(tq, tk, tv, cu, ms, inv_temp=inv_temp, zero_start=zero_start,
+                            attend_current=attend_current)
+    dq, dk, dv = torch.autograd.grad([o, rem], [tq, tk, tv], [tdo, tdr])
+    torch.cuda.synchronize()
+    return [x.detach().double().cpu().numpy() for x in (o, rem, dq, dk, dv)]
+
+
+def run_batched(q, k, v, do, drem, inv_temp, attend_current, dtype):
+    from stickbreaking_attention_b200 import sb_attn
+    tq, tk, tv = (to_dev(x, dtype).requires_grad_() for x in (q, k, v))
+    tdo, tdr = to_dev(do, dtype), to_dev(drem, dtype)
+    o, rem = sb_attn(tq, tk, tv, inv_temp=inv_temp, attend_current=attend_current)
+    dq, dk, dv = torch.autograd.grad([o, rem], [tq, tk, tv], [tdo, tdr])
+    torch.cuda.synchronize()
+    return [x.detach().double().cpu().numpy() for x in (o, rem, dq, dk, dv)]
+
+
+def oracle_varlen(q, k, v, do, drem, lengths, inv_temp, attend_current):
+    return orc.sb_varlen_fwd_bwd(q, k, v, do, drem, orc.ends_from_lengths(lengths), inv_temp, attend_current,
+                                 np.float64)
+
+
+def assert_close(names, got, want, tol, what=""):
+    for n, g, w in zip(names, got, want):
+        assert np.isfinite(g).all(), (what, n, "non-finite output")
+        err = np.abs(g - w).max() if g.size else 0.0
+        assert err <= tol, (what, n, float(err), tol)
+
+
+def rounded(x, dtype):
+    """numpy float32 array rounded to dtype and back (what the kernel sees)."""
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dtype).float().numpy()
+
+
+def synth(H, T, D, seed, dist="normal", scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+
+    def randn(*s):
+        return torch.randn(*s, generator=g, dtype=torch.float32)
+
+    if dist == "normal":
+        q, k, v = randn(H, T, D) * scale, randn(H, T, D) * scale, randn(H, T, D) * scale
+    else:
+        v = 0.25 * randn(H, T, D)
+        q = 0.25 * (randn(H, T, D) + 1)
+        k = 0.25 * (randn(H, T, D) - 1)
+    do, drem = randn(H, T, D), randn(H, T)
+    return [x.numpy() for x in (q, k, v, do, drem)]
