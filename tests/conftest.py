@@ -3,6 +3,9 @@ import sys
 
 import pytest
 
+# make every operator call synchronise and raise if a kernel reported a problem through its status word
+os.environ.setdefault("SBATTN_CHECK_STATUS", "1")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 for p in (ROOT, os.path.join(ROOT, "tests", "golden")):
     if p not in sys.path:
