@@ -51,6 +51,11 @@ extern "C" {
 #define SBATTN_PATH_SIMT 1   /* fp32-arithmetic kernels: any dtype, any head_dim <= 128, any strides     */
 #define SBATTN_PATH_TENSOR 2 /* tcgen05 kernels or SBATTN_EUNSUPPORTED / SBATTN_EALIGN                   */
 
+/* backward phases */
+#define SBATTN_BWD_ALL 0
+#define SBATTN_BWD_DQ 1
+#define SBATTN_BWD_DKDV 2
+
 /* [B,H,T,D] matrix (B absent for the packed layout); strides in ELEMENTS, the D stride is 1 */
 typedef struct SbMat {
     void* ptr;
@@ -77,6 +82,9 @@ typedef struct SbParams {
     int32_t attend_current; /* 0: key j < query i; 1: key j <= i                                          */
     float inv_temp;         /* logits = q.k * inv_temp                                                    */
     int32_t save_carries;   /* forward: 1 if a backward will follow (fills the carry part of fwd_workspace) */
+    int32_t bwd_phases;     /* backward: 0 = everything; SBATTN_BWD_DQ / SBATTN_BWD_DKDV run one kernel only
+                               (for timing them apart; dk/dv needs the carries the dq kernel leaves behind)   */
+    int32_t reserved;
 
     SbMat q, k, v;          /* inputs                                                                     */
     SbMat o;                /* forward output, dtype                                                      */

@@ -27,6 +27,7 @@ class SbParams(ctypes.Structure):
         ("tokens", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("num_seqs", ctypes.c_int32),
         ("cu_width", ctypes.c_int32), ("cu_seqlens", ctypes.c_void_p), ("max_seqlen", ctypes.c_int32),
         ("attend_current", ctypes.c_int32), ("inv_temp", ctypes.c_float), ("save_carries", ctypes.c_int32),
+        ("bwd_phases", ctypes.c_int32), ("reserved", ctypes.c_int32),
         ("q", SbMat), ("k", SbMat), ("v", SbMat), ("o", SbMat), ("rem", SbVec), ("neg_log_acc", SbVec),
         ("d_o", SbMat), ("d_rem", SbVec), ("dq", SbMat), ("dk", SbMat), ("dv", SbMat),
         ("fwd_workspace", ctypes.c_void_p), ("fwd_workspace_bytes", ctypes.c_size_t),

@@ -21,6 +21,7 @@ int check_shape(const SbParams* p) {
     if (p->dtype != SBATTN_BF16 && p->dtype != SBATTN_F32 && p->dtype != SBATTN_F16) return SBATTN_EINVAL;
     if (p->path != SBATTN_PATH_AUTO && p->path != SBATTN_PATH_SIMT && p->path != SBATTN_PATH_TENSOR)
         return SBATTN_EINVAL;
+    if (p->bwd_phases < 0 || p->bwd_phases > 2) return SBATTN_EINVAL;
     if (p->batch < 0 || p->heads < 0 || p->tokens < 0 || p->head_dim <= 0) return SBATTN_EINVAL;
     if (p->head_dim > kMaxHeadDim) return SBATTN_EUNSUPPORTED;
     if (p->batch == 0) {

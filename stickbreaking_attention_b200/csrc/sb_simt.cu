@@ -440,17 +440,17 @@ int launch_fwd_t(const WsLayout& L, const KArgs& a, cudaStream_t st) {
 }
 
 template <typename T>
-int launch_bwd_t(const WsLayout& L, const KArgs& a, cudaStream_t st) {
+int launch_bwd_t(const WsLayout& L, const KArgs& a, int phases, cudaStream_t st) {
     const size_t smem = simt_smem_bytes(a.head_dim, true);
     cudaError_t e = cudaFuncSetAttribute(simt_bwd_dq_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(simt_bwd_dkdv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(L.max_items, a.heads, 2);
-    simt_bwd_dq_kernel<T><<<grid, kThreads, smem, st>>>(a);
+    if (phases != SBATTN_BWD_DKDV) simt_bwd_dq_kernel<T><<<grid, kThreads, smem, st>>>(a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    simt_bwd_dkdv_kernel<T><<<grid, kThreads, smem, st>>>(a);
+    if (phases != SBATTN_BWD_DQ) simt_bwd_dkdv_kernel<T><<<grid, kThreads, smem, st>>>(a);
     return (int)cudaGetLastError();
 }
 
@@ -468,9 +468,9 @@ int launch_simt_fwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaSt
 int launch_simt_bwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st) {
     if (L.max_items <= 0) return 0;
     switch (p.dtype) {
-        case SBATTN_BF16: return launch_bwd_t<__nv_bfloat16>(L, a, st);
-        case SBATTN_F16: return launch_bwd_t<__half>(L, a, st);
-        default: return launch_bwd_t<float>(L, a, st);
+        case SBATTN_BF16: return launch_bwd_t<__nv_bfloat16>(L, a, p.bwd_phases, st);
+        case SBATTN_F16: return launch_bwd_t<__half>(L, a, p.bwd_phases, st);
+        default: return launch_bwd_t<float>(L, a, p.bwd_phases, st);
     }
 }
 

@@ -166,7 +166,8 @@ def _forward(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_curr
     return o, rem, neg_log_acc, ws
 
 
-def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current):
+def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current, phases=0,
+              out=None, bwd_ws=None):
     _require_cuda(q, k, v, do, dr, ws)
     q, k, v, do = _unit_inner(q), _unit_inner(k), _unit_inner(v), _unit_inner(do)
     if do.dtype != q.dtype:
@@ -174,14 +175,18 @@ def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale
     if dr.dtype != q.dtype:
         dr = dr.to(q.dtype)
     with torch.cuda.device(q.device):
-        dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
-        if dq.stride(-1) != 1:
-            dq, dk, dv = (torch.zeros(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
+        if out is not None:
+            dq, dk, dv = out
+        else:
+            dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+            if dq.stride(-1) != 1:
+                dq, dk, dv = (torch.zeros(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
         p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, True)
+        p.bwd_phases = phases
         fwd_bytes, bwd_bytes = _workspace_sizes(p)
         if ws.numel() < fwd_bytes:
             raise ValueError("the forward workspace does not belong to this problem (was the forward run with no_grad?)")
-        bws = torch.empty(bwd_bytes, dtype=torch.uint8, device=q.device)
+        bws = bwd_ws if bwd_ws is not None else torch.empty(bwd_bytes, dtype=torch.uint8, device=q.device)
         p.q, p.k, p.v = _mat(q, batched), _mat(k, batched), _mat(v, batched)
         p.d_o, p.d_rem = _mat(do, batched), _vec(dr, batched)
         p.dq, p.dk, p.dv = _mat(dq, batched), _mat(dk, batched), _mat(dv, batched)
@@ -202,12 +207,15 @@ def varlen_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=Fal
     return _forward(q, k, v, False, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad)
 
 
-def varlen_bwd(do, dr, q, k, v, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current=False):
+def varlen_bwd(do, dr, q, k, v, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current=False, phases=0,
+               out=None, bwd_workspace=None):
     """Returns (dq, dk, dv).  Mirrors varlen_bwd of the reference (sb_varlen_bwd.py:483-539); ``workspace`` takes
-    the place of its ``neg_log_acc`` argument."""
+    the place of its ``neg_log_acc`` argument.  ``phases`` (1: dq kernel only, 2: dk/dv kernel only), ``out`` and
+    ``bwd_workspace`` exist for benchmarking the two backward kernels apart; leave them at their defaults."""
     _check_qkv(q, k, v, 3)
     cu_seqlens, max_seqlens = _prep_cu(cu_seqlens, q, max_seqlens)
-    return _backward(do, dr, q, k, v, False, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current)
+    return _backward(do, dr, q, k, v, False, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current, phases,
+                     out, bwd_workspace)
 
 
 def attn_fwd(q, k, v, logit_scale, attend_current=False, no_grad=False):

@@ -155,20 +155,43 @@ def test_bitwise_deterministic():
 
 
 def test_bad_seqlens_reported_not_faulting():
+    """Sequence ends that decrease or run past the token count set a status bit; nothing is computed, nothing faults."""
     import stickbreaking_attention_b200 as sb
     from stickbreaking_attention_b200 import sb_attn_varlen
     H, T, D = 1, 256, 64
     q = torch.randn(H, T, D, device="cuda", dtype=torch.bfloat16)
     sb.check_status()
-    cu = torch.tensor([200, 100], device="cuda")  # decreasing
-    sb_attn_varlen(q, q, q, cu, 256, zero_start=False)
-    with pytest.raises(ValueError):
-        sb.check_status()
-    cu = torch.tensor([100, 300], device="cuda")  # beyond T
-    sb_attn_varlen(q, q, q, cu, 256, zero_start=False)
-    with pytest.raises(ValueError):
-        sb.check_status()
+    for ends in ([200, 100], [100, 300]):
+        cu = torch.tensor(ends, device="cuda")
+        with pytest.raises(ValueError):
+            sb_attn_varlen(q, q, q, cu, 256, zero_start=False)
+            sb.check_status()
     assert sb.check_status() == 0
+    o, rem = sb_attn_varlen(q, q, q, torch.tensor([100, 256], device="cuda"), 256, zero_start=False)
+    assert sb.check_status() == 0 and torch.isfinite(o.float()).all()
+
+
+def test_tensor_core_path_is_taken():
+    """Forcing the tcgen05 kernels must succeed for bf16/f16 with head_dim 64/128 and be refused otherwise."""
+    import stickbreaking_attention_b200 as sb
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    from stickbreaking_attention_b200._lib import SbAttnError
+    cu = torch.tensor([300], device="cuda")
+    sb.set_path("tensor")
+    try:
+        for D in (64, 128):
+            q = torch.randn(2, 300, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+            o, rem = sb_attn_varlen(q, q, q, cu, 300, zero_start=False)
+            (o.float().sum() + rem.float().sum()).backward()
+            assert torch.isfinite(q.grad.float()).all()
+        q = torch.randn(2, 300, 48, device="cuda", dtype=torch.bfloat16)
+        with pytest.raises(SbAttnError):
+            sb_attn_varlen(q, q, q, cu, 300, zero_start=False)
+        q = torch.randn(2, 300, 64, device="cuda", dtype=torch.float32)
+        with pytest.raises(SbAttnError):
+            sb_attn_varlen(q, q, q, cu, 300, zero_start=False)
+    finally:
+        sb.set_path("auto")
 
 
 def test_empty_and_no_grad():
