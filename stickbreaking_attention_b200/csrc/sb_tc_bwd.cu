@@ -1,0 +1,618 @@
+// Tensor-core backward (sm_100a) for bf16 / f16 inputs with head_dim 64 or 128: two kernels, no atomics and no
+// locks on dq, dk, dv (the reference accumulates dk/dv tiles in global memory under a spin lock,
+// stickbreaking_attention/sb_varlen/sb_varlen_bwd.py:11-53,454-465).
+//
+//   dq kernel     one work item = (head, sequence, 128-row query tile).  Walks the 64-key tiles LEFT TO RIGHT, the
+//                 direction of the reference's _backward_one_row (sb_varlen_bwd.py:401-473), because
+//                 ds_ik = g_ik - beta_ik * (sum of g over keys <= k) needs a prefix over the keys.  The weights of a
+//                 tile need the product W of (1 - beta) over everything to its right: the forward saved that value
+//                 for every 64-key boundary (carry_w).  The kernel leaves the prefix of g through the right edge
+//                 of every tile in carry_c for the second kernel.
+//   dk/dv kernel  one work item = (head, sequence, 64-key tile), kept stationary; walks the 128-row query tiles
+//                 below it.  Every (query tile, key tile) pair is entered directly with carry_w and carry_c, the
+//                 weights and ds are recomputed, written to shared memory as 16-bit operands, and
+//                 dv^T += do^T p, dk^T += q^T ds accumulate in tensor memory for the whole walk; stored once.
+//
+// Both kernels: 192 threads (warps 0-3: one thread per query row; warp 4: TMA; warp 5: tcgen05.mma), two
+// blocks per SM (256 tensor-memory columns each), persistent over the item table.
+#include "sb_tc_common.cuh"
+
+namespace sb {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kBM = 128;  // query rows per tile
+constexpr int kBK = 64;   // keys per tile
+constexpr uint32_t kTmemCols = 256;
+constexpr int kQBox = 128 * 128;  // bytes of one TMA box of a 128-row tile (64 elements wide)
+constexpr int kKBox = 64 * 128;   // bytes of one TMA box of a 64-row tile
+
+// element-wise core shared by both kernels: one score -> (1 - beta), beta
+template <bool kMasked>
+__device__ __forceinline__ void stick(float s, float scale, int col, int lim, float& om, float& beta) {
+    const float e = ex2_approx(s * scale);
+    om = rcp_approx(1.f + e);
+    beta = 1.f - om;
+    if (kMasked && col >= lim) { om = 1.f; beta = 0.f; }
+}
+
+// ================================================================================================ dq kernel
+enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_EMPTY0, A_K_EMPTY1, A_V_FULL, A_V_EMPTY, A_SDP_READY,
+             A_DS_READY, A_DQ_READY, A_DQ_FREE, kNumDqBars };
+
+template <bool kMasked>
+__device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[32], float scale, int col0, int lim,
+                                              float drem, float& W) {
+    // right to left: s <- beta, dp <- g = p * (dP - drem)
+#pragma unroll
+    for (int j = 31; j >= 0; --j) {
+        float om, beta;
+        stick<kMasked>(__uint_as_float(s[j]), scale, col0 + j, lim, om, beta);
+        const float p = beta * W;
+        W *= om;
+        dp[j] = __float_as_uint(p * (__uint_as_float(dp[j]) - drem));
+        s[j] = __float_as_uint(beta);
+    }
+}
+template <bool kF16>
+__device__ __forceinline__ void dq_half_pass2(const uint32_t (&beta)[32], const uint32_t (&g)[32], float& c,
+                                              uint32_t (&packed)[16]) {
+    // left to right: ds = g - beta * (inclusive prefix of g)
+    float ds[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        c += __uint_as_float(g[j]);
+        ds[j] = __uint_as_float(g[j]) - __uint_as_float(beta[j]) * c;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) packed[j] = pack16<kF16>(ds[2 * j], ds[2 * j + 1]);
+}
+
+template <int D, bool kF16>
+__global__ void __launch_bounds__(kThreads, 2)
+tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const KArgs a) {
+    constexpr int kBoxes = D / 64;
+    constexpr int kQBytes = kBM * D * 2, kKBytes = kBK * D * 2;
+    constexpr uint32_t kColS = 0, kColDP = 64, kColDQ = 128, kColDS = 0;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sQ = smem;
+    uint8_t* sDO = sQ + kQBytes;
+    uint8_t* sK = sDO + kQBytes;  // two stages
+    uint8_t* sV = sK + 2 * kKBytes;
+    uint64_t* bars = (uint64_t*)(sV + kKBytes);
+    uint32_t* tmem_slot = (uint32_t*)(bars + kNumDqBars);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int i = 0; i < kNumDqBars; ++i) mbar_init(&bars[i], (i == A_DS_READY || i == A_DQ_FREE) ? 128 : 1);
+        *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
+        fence_barrier_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 4 && lane == 0) {
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        tma_prefetch_desc(&map_do);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int n_work = *abort_flag ? 0 : a.hdr->n_items * a.heads;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            uint32_t ph_qe = 1, ph_ke[2] = {1, 1}, ph_ve = 1;
+            uint32_t kcount = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+                const Work wk = fetch_work(a, w);
+                const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
+                ok = mbar_wait(&bars[A_QDO_EMPTY], ph_qe, abort_flag);
+                ph_qe ^= 1;
+                if (!ok) break;
+                mbar_expect_tx(&bars[A_QDO_FULL], 2 * kQBytes);
+#pragma unroll
+                for (int bx = 0; bx < kBoxes; ++bx) {
+                    tma_load_4d(sQ + bx * kQBox, &map_q, &bars[A_QDO_FULL], bx * 64, wk.start + wk.qt * kBM, wk.h, wk.b);
+                    tma_load_4d(sDO + bx * kQBox, &map_do, &bars[A_QDO_FULL], bx * 64, wk.start + wk.qt * kBM, wk.h, wk.b);
+                }
+                for (int kh = 0; kh < n_kh; ++kh, ++kcount) {
+                    const int st = kcount & 1;
+                    const int row = wk.start + kh * kBK;
+                    ok = mbar_wait(&bars[A_K_EMPTY0 + st], ph_ke[st], abort_flag);
+                    ph_ke[st] ^= 1;
+                    if (!ok) break;
+                    mbar_expect_tx(&bars[A_K_FULL0 + st], kKBytes);
+#pragma unroll
+                    for (int bx = 0; bx < kBoxes; ++bx)
+                        tma_load_4d(sK + st * kKBytes + bx * kKBox, &map_k, &bars[A_K_FULL0 + st], bx * 64, row, wk.h, wk.b);
+                    ok = mbar_wait(&bars[A_V_EMPTY], ph_ve, abort_flag);
+                    ph_ve ^= 1;
+                    if (!ok) break;
+                    mbar_expect_tx(&bars[A_V_FULL], kKBytes);
+#pragma unroll
+                    for (int bx = 0; bx < kBoxes; ++bx)
+                        tma_load_4d(sV + bx * kKBox, &map_v, &bars[A_V_FULL], bx * 64, row, wk.h, wk.b);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc(kBM, kBK, kF16 ? 0 : 1, 0, 0);
+            constexpr uint32_t idesc_dq = make_idesc(kBM, D, kF16 ? 0 : 1, 0, 1);
+            const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+            uint32_t ph_qf = 0, ph_kf[2] = {0, 0}, ph_vf = 0, ph_ds = 0, ph_free = 1;
+            uint32_t kcount = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+                const Work wk = fetch_work(a, w);
+                const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
+                ok = mbar_wait(&bars[A_QDO_FULL], ph_qf, abort_flag);
+                ph_qf ^= 1;
+                if (!ok) break;
+                for (int t = 0; t < n_kh; ++t, ++kcount) {
+                    const int st = kcount & 1;
+                    const uint32_t ks = k_addr + st * kKBytes;
+                    ok = mbar_wait(&bars[A_K_FULL0 + st], ph_kf[st], abort_flag);
+                    ph_kf[st] ^= 1;
+                    if (!ok) break;
+                    ok = mbar_wait(&bars[A_V_FULL], ph_vf, abort_flag);
+                    ph_vf ^= 1;
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
+                        mma_ss(tmem + kColS, make_smem_desc(q_addr + oq, 0, 1024), make_smem_desc(ks + okk, 0, 1024),
+                               idesc_s, k > 0);
+                    }
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
+                        mma_ss(tmem + kColDP, make_smem_desc(do_addr + oq, 0, 1024), make_smem_desc(v_addr + okk, 0, 1024),
+                               idesc_s, k > 0);
+                    }
+                    mma_commit(&bars[A_SDP_READY]);
+                    mma_commit(&bars[A_V_EMPTY]);
+                    if (t == n_kh - 1) mma_commit(&bars[A_QDO_EMPTY]);
+                    ok = mbar_wait(&bars[A_DS_READY], ph_ds, abort_flag);
+                    ph_ds ^= 1;
+                    if (!ok) break;
+                    if (t == 0) {
+                        ok = mbar_wait(&bars[A_DQ_FREE], ph_free, abort_flag);
+                        ph_free ^= 1;
+                        if (!ok) break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k)
+                        mma_ts(tmem + kColDQ, tmem + kColDS + k * 8, make_smem_desc(ks + k * 2048, kKBox, 1024), idesc_dq,
+                               (t > 0 || k > 0) ? 1u : 0u);
+                    mma_commit(&bars[A_K_EMPTY0 + st]);
+                }
+                if (!ok) break;
+                mma_commit(&bars[A_DQ_READY]);
+            }
+        }
+    } else {
+        const int r = tid;
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const float scale = a.inv_temp * kLog2e;
+        uint32_t ph_sdp = 0, ph_dq = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+            const Work wk = fetch_work(a, w);
+            const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
+            const int qi = wk.qt * kBM + r;
+            const bool row_ok = qi < wk.len;
+            const int64_t tok = wk.start + qi;
+            float drem = 0.f;
+            if (row_ok) {
+                const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh + tok * a.d_rem.st);
+                drem = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
+            }
+            const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
+            float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
+            float cprefix = 0.f;
+            for (int kh = 0; kh < n_kh; ++kh) {
+                const int64_t slot = carry_slot(wk.slot_base, wk.qt, kh) * kTileQ;
+                float W = row_ok ? cw[slot] : 0.f;
+                ok = mbar_wait(&bars[A_SDP_READY], ph_sdp, abort_flag);
+                ph_sdp ^= 1;
+                if (!ok) break;
+                tc_fence_after();
+                const bool masked = kh >= 2 * wk.qt;  // the tile reaches the diagonal
+                const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
+                uint32_t s[32], dp[32], packed[16];
+                // right half: beta and g go back to tensor memory until the left half has been swept
+                tmem_ld32(lane_base + kColS + 32, s);
+                tmem_ld32(lane_base + kColDP + 32, dp);
+                tmem_wait_ld();
+                if (masked) dq_half_pass1<true>(s, dp, scale, 32, lim, drem, W);
+                else dq_half_pass1<false>(s, dp, scale, 32, lim, drem, W);
+                tmem_st32(lane_base + kColS + 32, s);
+                tmem_st32(lane_base + kColDP + 32, dp);
+                // left half
+                tmem_ld32(lane_base + kColS, s);
+                tmem_ld32(lane_base + kColDP, dp);
+                tmem_wait_ld();
+                if (masked) dq_half_pass1<true>(s, dp, scale, 0, lim, drem, W);
+                else dq_half_pass1<false>(s, dp, scale, 0, lim, drem, W);
+                float c = cprefix;
+                dq_half_pass2<kF16>(s, dp, c, packed);
+                tmem_wait_st();
+                tmem_st16(lane_base + kColDS, packed);
+                tmem_ld32(lane_base + kColS + 32, s);
+                tmem_ld32(lane_base + kColDP + 32, dp);
+                tmem_wait_ld();
+                dq_half_pass2<kF16>(s, dp, c, packed);
+                tmem_st16(lane_base + kColDS + 16, packed);
+                cprefix = c;
+                if (row_ok) cc[slot] = c;
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&bars[A_DS_READY]);
+            }
+            if (!ok) break;
+            ok = mbar_wait(&bars[A_DQ_READY], ph_dq, abort_flag);
+            ph_dq ^= 1;
+            if (!ok) break;
+            tc_fence_after();
+            char* orow = a.dq.ptr + 2 * ((int64_t)wk.b * a.dq.sb + (int64_t)wk.h * a.dq.sh + tok * a.dq.st);
+#pragma unroll
+            for (int cidx = 0; cidx < D / 32; ++cidx) {
+                uint32_t v[32];
+                tmem_ld32(lane_base + kColDQ + cidx * 32, v);
+                tmem_wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 u;
+                        uint32_t* up = (uint32_t*)&u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            up[j] = pack16<kF16>(__uint_as_float(v[g * 8 + 2 * j]) * a.inv_temp,
+                                                 __uint_as_float(v[g * 8 + 2 * j + 1]) * a.inv_temp);
+                        *(uint4*)(orow + (cidx * 32 + g * 8) * 2) = u;
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&bars[A_DQ_FREE]);
+        }
+    }
+    tc_teardown(abort_flag, a.status, tmem, kTmemCols, 5);
+}
+
+// ================================================================================================ dk/dv kernel
+enum KvBar { B_KV_FULL, B_KV_EMPTY, B_QDO_FULL, B_QDO_EMPTY, B_SDP_READY, B_PDS_TOP, B_PDS_BOT, B_BUF_FREE_A,
+             B_BUF_FREE_B, B_DKV_READY, B_DKV_FREE, kNumKvBars };
+
+struct KvWork {
+    int h, b, start, len, kh, slot_base, qt0, n_qt;
+    bool valid;
+};
+__device__ __forceinline__ KvWork fetch_kv_work(const KArgs& a, int n_items, int w) {
+    // key tiles are heaviest where query tiles are lightest: walk the item table backwards
+    const int per_item = 2 * a.heads;
+    const int idx = w / per_item, rem = w - idx * per_item;
+    const int half = rem / a.heads;
+    const int2 it = a.items[n_items - 1 - idx];
+    const SeqInfo s = a.seqs[it.x];
+    KvWork k;
+    k.h = rem - half * a.heads;
+    k.b = s.batch; k.start = s.start; k.len = s.len; k.slot_base = s.slot_base;
+    k.kh = 2 * it.y + half;
+    k.qt0 = it.y;
+    k.n_qt = (s.len + kBM - 1) / kBM;
+    k.valid = k.kh * kBK < s.len;
+    return k;
+}
+
+template <bool kMasked, bool kF16>
+__device__ __forceinline__ void kv_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], float scale, int col0, int lim,
+                                         float drem, float cright, float& W, float& sfx, uint32_t* pp, uint32_t* ps) {
+    // right to left over 32 columns: p and ds = g - beta * (cright - sum of g to the right)
+    float p[32], ds[32];
+#pragma unroll
+    for (int j = 31; j >= 0; --j) {
+        float om, beta;
+        stick<kMasked>(__uint_as_float(s[j]), scale, col0 + j, lim, om, beta);
+        p[j] = beta * W;
+        W *= om;
+        const float g = p[j] * (__uint_as_float(dp[j]) - drem);
+        ds[j] = g - beta * (cright - sfx);
+        sfx += g;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        pp[j] = pack16<kF16>(p[2 * j], p[2 * j + 1]);
+        ps[j] = pack16<kF16>(ds[2 * j], ds[2 * j + 1]);
+    }
+}
+
+template <int D, bool kF16>
+__global__ void __launch_bounds__(kThreads, 2)
+tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const KArgs a) {
+    constexpr int kBoxes = D / 64;
+    constexpr int kQBytes = kBM * D * 2, kKBytes = kBK * D * 2;
+    constexpr int kBufBytes = 64 * 128;  // 64 query rows x 64 keys, 16-bit
+    constexpr uint32_t kColS = 0, kColDP = 64, kColDK = 128, kColDV = 192;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sK = smem;
+    uint8_t* sV = sK + kKBytes;
+    uint8_t* sQ = sV + kKBytes;
+    uint8_t* sDO = sQ + kQBytes;
+    uint8_t* sP = sDO + kQBytes;
+    uint8_t* sDS = sP + kBufBytes;
+    uint64_t* bars = (uint64_t*)(sDS + kBufBytes);
+    uint32_t* tmem_slot = (uint32_t*)(bars + kNumKvBars);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int i = 0; i < kNumKvBars; ++i)
+            mbar_init(&bars[i], (i == B_PDS_TOP || i == B_PDS_BOT) ? 64 : (i == B_DKV_FREE ? 128 : 1));
+        *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;
+        fence_barrier_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 4 && lane == 0) {
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        tma_prefetch_desc(&map_do);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int n_items = a.hdr->n_items;
+    const int n_work = *abort_flag ? 0 : n_items * a.heads * 2;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            uint32_t ph_kve = 1, ph_qe = 1;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+                const KvWork wk = fetch_kv_work(a, n_items, w);
+                if (!wk.valid) continue;
+                ok = mbar_wait(&bars[B_KV_EMPTY], ph_kve, abort_flag);
+                ph_kve ^= 1;
+                if (!ok) break;
+                mbar_expect_tx(&bars[B_KV_FULL], 2 * kKBytes);
+#pragma unroll
+                for (int bx = 0; bx < kBoxes; ++bx) {
+                    tma_load_4d(sK + bx * kKBox, &map_k, &bars[B_KV_FULL], bx * 64, wk.start + wk.kh * kBK, wk.h, wk.b);
+                    tma_load_4d(sV + bx * kKBox, &map_v, &bars[B_KV_FULL], bx * 64, wk.start + wk.kh * kBK, wk.h, wk.b);
+                }
+                for (int i = wk.qt0; i < wk.n_qt; ++i) {
+                    ok = mbar_wait(&bars[B_QDO_EMPTY], ph_qe, abort_flag);
+                    ph_qe ^= 1;
+                    if (!ok) break;
+                    mbar_expect_tx(&bars[B_QDO_FULL], 2 * kQBytes);
+#pragma unroll
+                    for (int bx = 0; bx < kBoxes; ++bx) {
+                        tma_load_4d(sQ + bx * kQBox, &map_q, &bars[B_QDO_FULL], bx * 64, wk.start + i * kBM, wk.h, wk.b);
+                        tma_load_4d(sDO + bx * kQBox, &map_do, &bars[B_QDO_FULL], bx * 64, wk.start + i * kBM, wk.h, wk.b);
+                    }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc(kBM, kBK, kF16 ? 0 : 1, 0, 0);
+            constexpr uint32_t idesc_t = make_idesc(D, kBK, kF16 ? 0 : 1, 1, 1);  // (dO^T or Q^T)[D x q] * (P or dS)[q x 64]
+            const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+            const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+            uint32_t ph_kvf = 0, ph_qf = 0, ph_top = 0, ph_bot = 0, ph_free = 1;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+                const KvWork wk = fetch_kv_work(a, n_items, w);
+                if (!wk.valid) continue;
+                ok = mbar_wait(&bars[B_KV_FULL], ph_kvf, abort_flag);
+                ph_kvf ^= 1;
+                if (!ok) break;
+                for (int i = wk.qt0; i < wk.n_qt; ++i) {
+                    ok = mbar_wait(&bars[B_QDO_FULL], ph_qf, abort_flag);
+                    ph_qf ^= 1;
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
+                        mma_ss(tmem + kColS, make_smem_desc(q_addr + oq, 0, 1024), make_smem_desc(k_addr + okk, 0, 1024),
+                               idesc_s, k > 0);
+                    }
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
+                        mma_ss(tmem + kColDP, make_smem_desc(do_addr + oq, 0, 1024), make_smem_desc(v_addr + okk, 0, 1024),
+                               idesc_s, k > 0);
+                    }
+                    mma_commit(&bars[B_SDP_READY]);
+                    if (i == wk.n_qt - 1) mma_commit(&bars[B_KV_EMPTY]);
+                    if (i == wk.qt0) {  // the previous item's accumulators must have been read out
+                        ok = mbar_wait(&bars[B_DKV_FREE], ph_free, abort_flag);
+                        ph_free ^= 1;
+                        if (!ok) break;
+                    }
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        ok = mbar_wait(&bars[half == 0 ? B_PDS_TOP : B_PDS_BOT], half == 0 ? ph_top : ph_bot, abort_flag);
+                        if (half == 0) ph_top ^= 1; else ph_bot ^= 1;
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const uint32_t acc = (i > wk.qt0 || half > 0 || kk > 0) ? 1u : 0u;
+                            const uint32_t oa = (half * 4 + kk) * 2048, ob = kk * 2048;
+                            mma_ss(tmem + kColDV, make_smem_desc(do_addr + oa, kQBox, 1024), make_smem_desc(p_addr + ob, 0, 1024),
+                                   idesc_t, acc);
+                            mma_ss(tmem + kColDK, make_smem_desc(q_addr + oa, kQBox, 1024), make_smem_desc(ds_addr + ob, 0, 1024),
+                                   idesc_t, acc);
+                        }
+                        mma_commit(&bars[half == 0 ? B_BUF_FREE_A : B_BUF_FREE_B]);
+                    }
+                    if (!ok) break;
+                    mma_commit(&bars[B_QDO_EMPTY]);
+                }
+                if (!ok) break;
+                mma_commit(&bars[B_DKV_READY]);
+            }
+        }
+    } else {
+        const int r = tid;
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const float scale = a.inv_temp * kLog2e;
+        const bool top = warp < 2;
+        uint8_t* prow = sP + (r & 63) * 128;
+        uint8_t* srow = sDS + (r & 63) * 128;
+        uint32_t ph_sdp = 0, ph_buf = top ? 1 : 0, ph_dkv = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+            const KvWork wk = fetch_kv_work(a, n_items, w);
+            if (!wk.valid) continue;
+            const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
+            const float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
+            for (int i = wk.qt0; i < wk.n_qt; ++i) {
+                const int qi = i * kBM + r;
+                const bool row_ok = qi < wk.len;
+                float W = 0.f, cright = 0.f, drem = 0.f;
+                if (row_ok) {
+                    const int64_t slot = carry_slot(wk.slot_base, i, wk.kh) * kTileQ;
+                    W = cw[slot];
+                    cright = cc[slot];
+                    const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh +
+                                                        (int64_t)(wk.start + qi) * a.d_rem.st);
+                    drem = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
+                }
+                ok = mbar_wait(&bars[B_SDP_READY], ph_sdp, abort_flag);
+                ph_sdp ^= 1;
+                if (!ok) break;
+                tc_fence_after();
+                const bool masked = i == wk.qt0;
+                const int lim = min(kBK, max(0, qi - wk.kh * kBK + a.attend_current));
+                uint32_t pp[32], ps[32];
+                float sfx = 0.f;
+                {
+                    uint32_t s[32], dp[32];
+                    tmem_ld32(lane_base + kColS + 32, s);
+                    tmem_ld32(lane_base + kColDP + 32, dp);
+                    tmem_wait_ld();
+                    if (masked) kv_chunk<true, kF16>(s, dp, scale, 32, lim, drem, cright, W, sfx, pp + 16, ps + 16);
+                    else kv_chunk<false, kF16>(s, dp, scale, 32, lim, drem, cright, W, sfx, pp + 16, ps + 16);
+                    tmem_ld32(lane_base + kColS, s);
+                    tmem_ld32(lane_base + kColDP, dp);
+                    tmem_wait_ld();
+                    if (masked) kv_chunk<true, kF16>(s, dp, scale, 0, lim, drem, cright, W, sfx, pp, ps);
+                    else kv_chunk<false, kF16>(s, dp, scale, 0, lim, drem, cright, W, sfx, pp, ps);
+                }
+                tc_fence_before();
+                // rows 0-63 write first; rows 64-127 reuse the buffers once the first half has been consumed
+                ok = mbar_wait(&bars[top ? B_BUF_FREE_B : B_BUF_FREE_A], ph_buf, abort_flag);
+                ph_buf ^= 1;
+                if (!ok) break;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    const int off = (ch ^ (r & 7)) << 4;
+                    *(uint4*)(prow + off) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+                    *(uint4*)(srow + off) = make_uint4(ps[4 * ch], ps[4 * ch + 1], ps[4 * ch + 2], ps[4 * ch + 3]);
+                }
+                fence_async_smem();
+                mbar_arrive(&bars[top ? B_PDS_TOP : B_PDS_BOT]);
+            }
+            if (!ok) break;
+            // epilogue: this thread holds one head-dim index d of dk^T and dv^T, the 64 keys along the columns
+            ok = mbar_wait(&bars[B_DKV_READY], ph_dkv, abort_flag);
+            ph_dkv ^= 1;
+            if (!ok) break;
+            tc_fence_after();
+            const int d = D == 128 ? r : (warp * 16 + lane);
+            const bool d_ok = D == 128 ? true : lane < 16;
+            const int keys_valid = min(kBK, wk.len - wk.kh * kBK);
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                const MatView& m = which == 0 ? a.dk : a.dv;
+                const float sc = which == 0 ? a.inv_temp : 1.f;
+                char* base = m.ptr + 2 * ((int64_t)wk.b * m.sb + (int64_t)wk.h * m.sh +
+                                          (int64_t)(wk.start + wk.kh * kBK) * m.st + d);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_base + (which == 0 ? kColDK : kColDV) + half * 32, v);
+                    tmem_wait_ld();
+                    if (d_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int key = half * 32 + j;
+                            if (key < keys_valid) {
+                                const float x = __uint_as_float(v[j]) * sc;
+                                char* ptr = base + 2 * (int64_t)key * m.st;
+                                if (kF16) *(__half*)ptr = __float2half_rn(x);
+                                else *(__nv_bfloat16*)ptr = __float2bfloat16_rn(x);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&bars[B_DKV_FREE]);
+        }
+    }
+    tc_teardown(abort_flag, a.status, tmem, kTmemCols, 5);
+}
+
+template <int D, bool kF16>
+int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
+    CUtensorMap mq, mk, mv, mdo;
+    const int kind = kF16 ? 2 : 0;
+    const int64_t B = p.batch > 0 ? p.batch : 1;
+    if (encode_tile_map(&mq, p.q.ptr, kind, D, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBM) ||
+        encode_tile_map(&mdo, p.d_o.ptr, kind, D, p.tokens, p.heads, B, p.d_o.stride_t, p.d_o.stride_h, p.d_o.stride_b, kBM) ||
+        encode_tile_map(&mk, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBK) ||
+        encode_tile_map(&mv, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBK))
+        return 1;
+    // both kernels: 2 x (128 x D) + 3 x (64 x D) 16-bit tiles (dq: q, do, 2 k stages, v; dk/dv: k, v, q, do, p, ds)
+    constexpr int need = 2 * kBM * D * 2 + 3 * kBK * D * 2 + 256;
+    constexpr int need_b = 2 * kBM * D * 2 + 2 * kBK * D * 2 + 2 * 64 * 128 + 256;
+    // at least 80 KB so that never more than two blocks (2 x 256 tensor-memory columns) share an SM
+    constexpr int smem_a = need > 81920 ? need : 81920;
+    constexpr int smem_b = need_b > 81920 ? need_b : 81920;
+    cudaError_t e = cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_b);
+    if (e != cudaSuccess) return (int)e;
+    cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    const int grid = 2 * sm_count();
+    if (p.bwd_phases != SBATTN_BWD_DKDV) tc_bwd_dq_kernel<D, kF16><<<grid, kThreads, smem_a, st>>>(mq, mk, mv, mdo, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<grid, kThreads, smem_b, st>>>(mq, mk, mv, mdo, a);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+int launch_tensor_bwd_impl(const SbParams& p, const KArgs& a, cudaStream_t st) {
+    const bool f16 = p.dtype == SBATTN_F16;
+    if (p.head_dim == 128) return f16 ? launch_bwd_t<128, true>(p, a, st) : launch_bwd_t<128, false>(p, a, st);
+    return f16 ? launch_bwd_t<64, true>(p, a, st) : launch_bwd_t<64, false>(p, a, st);
+}
+
+}  // namespace sb

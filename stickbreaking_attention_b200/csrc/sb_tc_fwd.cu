@@ -17,8 +17,7 @@
 //              O += P V (P from TMEM columns [64,128), V from shared memory) into columns [128,128+D).
 // P overwrites the right half of S: a row is processed right to left in chunks of 32 columns and the packed
 // weights of chunk c land in columns that were already read.
-#include "sb_common.cuh"
-#include "sb_sm100.cuh"
+#include "sb_tc_common.cuh"
 
 namespace sb {
 
@@ -30,35 +29,7 @@ constexpr int kFwdThreads = 192;
 constexpr int kBM = 128, kBN = 128;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColP = 64, kColO = 128;
-constexpr float kLog2e = 1.4426950408889634f;
-
 enum FwdBar { Q_FULL, Q_EMPTY, K_FULL, K_EMPTY, V_FULL, V_EMPTY, S_READY, P_READY, O_READY, O_FREE, kNumBars };
-
-__device__ __forceinline__ float ex2_approx(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float rcp_approx(float x) {
-    float y;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float lg2_approx(float x) {
-    float y;
-    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-struct Work {
-    int h, b, start, len, qt, slot_base;
-};
-__device__ __forceinline__ Work fetch_work(const KArgs& a, int w) {
-    const int item = w / a.heads;
-    const int2 it = a.items[item];
-    const SeqInfo s = a.seqs[it.x];
-    return Work{w - item * a.heads, s.batch, s.start, s.len, it.y, s.slot_base};
-}
 
 template <int D, bool kF16>
 __global__ void __launch_bounds__(kFwdThreads, 2)
@@ -282,32 +253,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             }
         }
     }
-    // ---------------------------------------------------------------------- teardown
-    __syncwarp();
-    tc_fence_before();
-    __syncthreads();
-    if (*abort_flag) {
-        if (tid == 0) atomicOr(a.status, SBATTN_ST_TIMEOUT);
-        // give copies that may still be in flight time to land before the shared memory is released
-        for (int i = 0; i < 200; ++i) __nanosleep(5000);
-        __syncthreads();
-    }
-    if (warp == 5) {
-        tc_fence_after();
-        tmem_dealloc(tmem, kTmemCols);
-    }
-}
-
-int g_sm_count[64] = {0};
-int sm_count() {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (g_sm_count[dev] == 0) {
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        g_sm_count[dev] = n;
-    }
-    return g_sm_count[dev];
+    tc_teardown(abort_flag, a.status, tmem, kTmemCols, 5);
 }
 
 template <int D, bool kF16>
@@ -323,13 +269,9 @@ int launch_fwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     constexpr int smem = (3 * kBM * D * 2 + 1024 + 256) > 81920 ? (3 * kBM * D * 2 + 1024 + 256) : 81920;
     cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
+    cudaFuncSetAttribute(tc_fwd_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     tc_fwd_kernel<D, kF16><<<2 * sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
     return (int)cudaGetLastError();
-}
-
-bool aligned_mat(const SbMat& m) {
-    if (!m.ptr) return true;
-    return ((uintptr_t)m.ptr & 15) == 0 && (m.stride_t & 7) == 0 && (m.stride_h & 7) == 0 && (m.stride_b & 7) == 0;
 }
 
 }  // namespace
@@ -338,9 +280,14 @@ bool tensor_path_eligible(const SbParams& p, bool backward, int* why) {
     *why = SBATTN_EUNSUPPORTED;
     if (p.dtype != SBATTN_BF16 && p.dtype != SBATTN_F16) return false;
     if (p.head_dim != 64 && p.head_dim != 128) return false;
-    if (backward) return false;  // tensor-core backward not built yet
     *why = SBATTN_EALIGN;
-    if (!aligned_mat(p.q) || !aligned_mat(p.k) || !aligned_mat(p.v) || !aligned_mat(p.o)) return false;
+    if (!aligned_mat(p.q) || !aligned_mat(p.k) || !aligned_mat(p.v)) return false;
+    if (backward) {
+        if (!aligned_mat(p.d_o) || !aligned_mat(p.dq) || !aligned_mat(p.dk) || !aligned_mat(p.dv)) return false;
+        if (p.d_o.stride_t < p.head_dim) return false;
+    } else if (!aligned_mat(p.o)) {
+        return false;
+    }
     if (p.q.stride_t < p.head_dim || p.k.stride_t < p.head_dim || p.v.stride_t < p.head_dim) return false;
     return true;
 }
@@ -351,6 +298,8 @@ int launch_tensor_fwd(const SbParams& p, const WsLayout&, const KArgs& a, cudaSt
     return f16 ? launch_fwd_t<64, true>(p, a, st) : launch_fwd_t<64, false>(p, a, st);
 }
 
-int launch_tensor_bwd(const SbParams&, const WsLayout&, const KArgs&, cudaStream_t) { return 1; }
+int launch_tensor_bwd(const SbParams& p, const WsLayout&, const KArgs& a, cudaStream_t st) {
+    return launch_tensor_bwd_impl(p, a, st);
+}
 
 }  // namespace sb
