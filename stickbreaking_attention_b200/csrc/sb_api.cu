@@ -51,6 +51,12 @@ KArgs make_args(const SbParams& p, const WsLayout& L) {
     a.head_dim = p.head_dim;
     a.attend_current = p.attend_current ? 1 : 0;
     a.inv_temp = p.inv_temp;
+    a.sched = ((WsHeader*)ws)->sched;
+    {   // heads worked on together: their K and V (2 x T x D 16-bit values each) should fit in a third of the L2
+        const int64_t per_head = (int64_t)p.tokens * p.head_dim * 4;
+        int64_t g = per_head > 0 ? (40ll << 20) / per_head : 8;
+        a.head_group = (int32_t)(g < 1 ? 1 : (g > 8 ? 8 : g));
+    }
     a.q = view(p.q); a.k = view(p.k); a.v = view(p.v); a.o = view(p.o);
     a.d_o = view(p.d_o); a.dq = view(p.dq); a.dk = view(p.dk); a.dv = view(p.dv);
     a.rem = view(p.rem); a.nla = view(p.neg_log_acc); a.d_rem = view(p.d_rem);

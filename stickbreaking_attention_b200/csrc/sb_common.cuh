@@ -29,7 +29,10 @@ struct WsHeader {
     int32_t n_seqs;
     int32_t total_slots;  // carry slots per head actually used
     int32_t bad;          // non-zero: sequence table rejected, n_items is 0
-    int32_t pad[60];
+    // work counters of the persistent kernels (forward, backward dq, backward dk/dv): [2k] next work index,
+    // [2k+1] blocks that have finished; zeroed by the prep kernel, reset by the last block of every launch
+    int32_t sched[8];
+    int32_t pad[52];
 };
 static_assert(sizeof(WsHeader) == 256, "header is one 256-byte line");
 
@@ -99,6 +102,8 @@ struct KArgs {
     float* carry_c;         // backward carries [heads][slot_cap][128]
     int64_t slot_cap;
     int32_t heads, head_dim, attend_current;
+    int32_t head_group;     // heads whose work is interleaved (sized so that their K and V stay in L2)
+    int32_t* sched;         // WsHeader::sched
     float inv_temp;
     MatView q, k, v, o, d_o, dq, dk, dv;
     VecView rem, nla, d_rem;

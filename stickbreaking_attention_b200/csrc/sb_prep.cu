@@ -50,6 +50,7 @@ prep_kernel(WsHeader* hdr, SeqInfo* seqs, int2* items, int32_t* bins, const void
     int32_t* count = bins;               // [n_max+2] sequences per tile count, then items per cost class
     int32_t* cursor = bins + n_max + 2;  // [n_max+2] write position per cost class
     if (t == 0) sh_bad = 0;
+    if (t < 8) hdr->sched[t] = 0;
     for (int i = t; i < 2 * (n_max + 2); i += kPrepThreads) bins[i] = 0;
     __syncthreads();
 

@@ -41,7 +41,7 @@ __device__ __forceinline__ void stick(float s, float scale, int col, int lim, fl
 
 // ================================================================================================ dq kernel
 enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_EMPTY0, A_K_EMPTY1, A_V_FULL, A_V_EMPTY, A_SDP_READY,
-             A_DS_READY, A_DQ_READY, A_DQ_FREE, kNumDqBars };
+             A_DS_READY, A_DQ_READY, A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1, kNumDqBars };
 
 template <bool kMasked>
 __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[32], float scale, int col0, int lim,
@@ -86,10 +86,13 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint64_t* bars = (uint64_t*)(sV + kKBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumDqBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    SchedRing* ring = (SchedRing*)(tmem_slot + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int i = 0; i < kNumDqBars; ++i) mbar_init(&bars[i], (i == A_DS_READY || i == A_DQ_FREE) ? 128 : 1);
+        for (int i = 0; i < kNumDqBars; ++i)
+            mbar_init(&bars[i], (i == A_DS_READY || i == A_DQ_FREE) ? 128
+                                : ((i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) ? kRingConsumers : 1));
         *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
         fence_barrier_init();
     }
@@ -107,15 +110,18 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const int n_work = *abort_flag ? 0 : a.hdr->n_items * a.heads;
+    const int n_items = a.hdr->n_items;
+    const int n_work = *abort_flag ? 0 : n_items * a.heads;
 
     if (warp == 4) {
         if (lane == 0) {
             uint32_t ph_qe = 1, ph_ke[2] = {1, 1}, ph_ve = 1;
             uint32_t kcount = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
-                const Work wk = fetch_work(a, w);
+            SchedProducer sched;
+            int w;
+            while (ok && (w = sched.next(a.sched + 2, n_work, ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag)) >= 0) {
+                const Work wk = fetch_work(a, n_items, w);
                 const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
                 ok = mbar_wait(&bars[A_QDO_EMPTY], ph_qe, abort_flag);
                 ph_qe ^= 1;
@@ -154,8 +160,10 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             uint32_t ph_qf = 0, ph_kf[2] = {0, 0}, ph_vf = 0, ph_ds = 0, ph_free = 1;
             uint32_t kcount = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
-                const Work wk = fetch_work(a, w);
+            SchedConsumer sched;
+            int w;
+            while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag)) >= 0) {
+                const Work wk = fetch_work(a, n_items, w);
                 const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
                 ok = mbar_wait(&bars[A_QDO_FULL], ph_qf, abort_flag);
                 ph_qf ^= 1;
@@ -210,8 +218,10 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const float scale = a.inv_temp * kLog2e;
         uint32_t ph_sdp = 0, ph_dq = 0;
         bool ok = true;
-        for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
-            const Work wk = fetch_work(a, w);
+        SchedConsumer sched;
+        int w;
+        while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag)) >= 0) {
+            const Work wk = fetch_work(a, n_items, w);
             const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
             const int qi = wk.qt * kBM + r;
             const bool row_ok = qi < wk.len;
@@ -224,9 +234,11 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             float cprefix = 0.f;
+            float W_next = row_ok ? cw[carry_slot(wk.slot_base, wk.qt, 0) * kTileQ] : 0.f;
             for (int kh = 0; kh < n_kh; ++kh) {
                 const int64_t slot = carry_slot(wk.slot_base, wk.qt, kh) * kTileQ;
-                float W = row_ok ? cw[slot] : 0.f;
+                float W = W_next;
+                if (row_ok && kh + 1 < n_kh) W_next = cw[slot + kTileQ];  // carry of the next tile: in flight during this one
                 ok = mbar_wait(&bars[A_SDP_READY], ph_sdp, abort_flag);
                 ph_sdp ^= 1;
                 if (!ok) break;
@@ -292,25 +304,30 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
     }
     tc_teardown(abort_flag, a.status, tmem, kTmemCols, 5);
+    sched_finish(a.sched + 2);
 }
 
 // ================================================================================================ dk/dv kernel
 enum KvBar { B_KV_FULL, B_KV_EMPTY, B_QDO_FULL, B_QDO_EMPTY, B_SDP_READY, B_PDS_TOP, B_PDS_BOT, B_BUF_FREE_A,
-             B_BUF_FREE_B, B_DKV_READY, B_DKV_FREE, kNumKvBars };
+             B_BUF_FREE_B, B_DKV_READY, B_DKV_FREE, B_WORK_FULL0, B_WORK_FULL1, B_WORK_EMPTY0, B_WORK_EMPTY1, kNumKvBars };
 
 struct KvWork {
     int h, b, start, len, kh, slot_base, qt0, n_qt;
     bool valid;
 };
 __device__ __forceinline__ KvWork fetch_kv_work(const KArgs& a, int n_items, int w) {
-    // key tiles are heaviest where query tiles are lightest: walk the item table backwards
-    const int per_item = 2 * a.heads;
-    const int idx = w / per_item, rem = w - idx * per_item;
-    const int half = rem / a.heads;
+    // groups of head_group heads; inside a group the 64-key tiles heaviest first (key tiles are heaviest where
+    // query tiles are lightest: the item table is walked backwards), the two halves of a 128-row item and the heads
+    // of the group innermost
+    const int per_group = n_items * 2 * a.head_group;
+    const int g = w / per_group, rest = w - g * per_group;
+    const int hg = min(a.head_group, a.heads - g * a.head_group);
+    const int idx = rest / (2 * hg), rem = rest - idx * 2 * hg;
+    const int half = rem / hg;
     const int2 it = a.items[n_items - 1 - idx];
     const SeqInfo s = a.seqs[it.x];
     KvWork k;
-    k.h = rem - half * a.heads;
+    k.h = g * a.head_group + rem - half * hg;
     k.b = s.batch; k.start = s.start; k.len = s.len; k.slot_base = s.slot_base;
     k.kh = 2 * it.y + half;
     k.qt0 = it.y;
@@ -359,11 +376,13 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint64_t* bars = (uint64_t*)(sDS + kBufBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumKvBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    SchedRing* ring = (SchedRing*)(tmem_slot + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < kNumKvBars; ++i)
-            mbar_init(&bars[i], (i == B_PDS_TOP || i == B_PDS_BOT) ? 64 : (i == B_DKV_FREE ? 128 : 1));
+            mbar_init(&bars[i], (i == B_PDS_TOP || i == B_PDS_BOT) ? 64
+                                : (i == B_DKV_FREE ? 128 : ((i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) ? kRingConsumers : 1)));
         *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;
         fence_barrier_init();
     }
@@ -388,7 +407,9 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (lane == 0) {
             uint32_t ph_kve = 1, ph_qe = 1;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+            SchedProducer sched;
+            int w;
+            while (ok && (w = sched.next(a.sched + 4, n_work, ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
                 const KvWork wk = fetch_kv_work(a, n_items, w);
                 if (!wk.valid) continue;
                 ok = mbar_wait(&bars[B_KV_EMPTY], ph_kve, abort_flag);
@@ -421,7 +442,9 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
             uint32_t ph_kvf = 0, ph_qf = 0, ph_top = 0, ph_bot = 0, ph_free = 1;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+            SchedConsumer sched;
+            int w;
+            while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
                 const KvWork wk = fetch_kv_work(a, n_items, w);
                 if (!wk.valid) continue;
                 ok = mbar_wait(&bars[B_KV_FULL], ph_kvf, abort_flag);
@@ -484,23 +507,33 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         uint8_t* srow = sDS + (r & 63) * 128;
         uint32_t ph_sdp = 0, ph_buf = top ? 1 : 0, ph_dkv = 0;
         bool ok = true;
-        for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+        SchedConsumer sched;
+        int w;
+        while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
             const KvWork wk = fetch_kv_work(a, n_items, w);
             if (!wk.valid) continue;
             const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             const float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
-            for (int i = wk.qt0; i < wk.n_qt; ++i) {
+            // per-row scalars of a step (carry of W, prefix of g, drem): loaded one step ahead
+            float nW = 0.f, nC = 0.f, nD = 0.f;
+            auto load_scalars = [&](int i) {
                 const int qi = i * kBM + r;
-                const bool row_ok = qi < wk.len;
-                float W = 0.f, cright = 0.f, drem = 0.f;
-                if (row_ok) {
+                nW = 0.f; nC = 0.f; nD = 0.f;
+                if (i < wk.n_qt && qi < wk.len) {
                     const int64_t slot = carry_slot(wk.slot_base, i, wk.kh) * kTileQ;
-                    W = cw[slot];
-                    cright = cc[slot];
+                    nW = cw[slot];
+                    nC = cc[slot];
                     const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh +
                                                         (int64_t)(wk.start + qi) * a.d_rem.st);
-                    drem = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
+                    nD = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
                 }
+            };
+            load_scalars(wk.qt0);
+            for (int i = wk.qt0; i < wk.n_qt; ++i) {
+                const int qi = i * kBM + r;
+                float W = nW;
+                const float cright = nC, drem = nD;
+                load_scalars(i + 1);
                 ok = mbar_wait(&bars[B_SDP_READY], ph_sdp, abort_flag);
                 ph_sdp ^= 1;
                 if (!ok) break;
@@ -575,6 +608,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
     }
     tc_teardown(abort_flag, a.status, tmem, kTmemCols, 5);
+    sched_finish(a.sched + 4);
 }
 
 template <int D, bool kF16>

@@ -29,15 +29,68 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     return kF16 ? sm100::pack_f16(lo, hi) : sm100::pack_bf16(lo, hi);
 }
 
-// (head, sequence, 128-row tile) of a flat work index; items are ordered heaviest first
+// (head, sequence, 128-row tile) of a flat work index.  Order: groups of `head_group` heads; inside a group the
+// items heaviest first, the heads of the group innermost.
 struct Work {
     int h, b, start, len, qt, slot_base;
 };
-__device__ __forceinline__ Work fetch_work(const KArgs& a, int w) {
-    const int item = w / a.heads;
+__device__ __forceinline__ Work fetch_work(const KArgs& a, int n_items, int w) {
+    const int per_group = n_items * a.head_group;
+    const int g = w / per_group, rest = w - g * per_group;
+    const int hg = min(a.head_group, a.heads - g * a.head_group);
+    const int item = rest / hg;
     const int2 it = a.items[item];
     const SeqInfo s = a.seqs[it.x];
-    return Work{w - item * a.heads, s.batch, s.start, s.len, it.y, s.slot_base};
+    return Work{g * a.head_group + rest - item * hg, s.batch, s.start, s.len, it.y, s.slot_base};
+}
+
+// ---------------------------------------------------------------------------------------------- work scheduler
+// One thread of the block (the TMA producer) draws work indices from a global counter and hands them to the MMA
+// thread and the 128 row threads through a two-slot ring in shared memory.  A negative index ends the block.
+constexpr int kRing = 2;
+constexpr int kRingConsumers = 129;  // 1 MMA thread + 128 row threads
+struct SchedRing {
+    int32_t slot[kRing];
+};
+struct SchedProducer {
+    int i = 0;
+    uint32_t ph[kRing] = {1, 1};
+    __device__ __forceinline__ int next(int32_t* counter, int n_work, SchedRing* ring, uint64_t* full, uint64_t* empty,
+                                        volatile uint32_t* abort_flag) {
+        const int sl = i & (kRing - 1);
+        ++i;
+        if (!sm100::mbar_wait(&empty[sl], ph[sl], abort_flag)) return -1;
+        ph[sl] ^= 1;
+        int w = atomicAdd(counter, 1);
+        if (w >= n_work) w = -1;
+        ring->slot[sl] = w;
+        sm100::mbar_arrive(&full[sl]);
+        return w;
+    }
+};
+struct SchedConsumer {
+    int i = 0;
+    uint32_t ph[kRing] = {0, 0};
+    __device__ __forceinline__ int next(SchedRing* ring, uint64_t* full, uint64_t* empty, volatile uint32_t* abort_flag) {
+        const int sl = i & (kRing - 1);
+        ++i;
+        if (!sm100::mbar_wait(&full[sl], ph[sl], abort_flag)) return -1;
+        ph[sl] ^= 1;
+        const int w = ((volatile SchedRing*)ring)->slot[sl];
+        sm100::mbar_arrive(&empty[sl]);
+        return w;
+    }
+};
+// the last block to finish re-arms the counters for the next launch
+__device__ __forceinline__ void sched_finish(int32_t* counter) {
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(counter + 1, 1) == (int)gridDim.x - 1) {
+            counter[0] = 0;
+            counter[1] = 0;
+            __threadfence();
+        }
+    }
 }
 
 // teardown shared by the kernels: report a wait that ran out, let copies in flight land, free tensor memory

@@ -29,7 +29,37 @@ constexpr int kFwdThreads = 192;
 constexpr int kBM = 128, kBN = 128;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColP = 64, kColO = 128;
-enum FwdBar { Q_FULL, Q_EMPTY, K_FULL, K_EMPTY, V_FULL, V_EMPTY, S_READY, P_READY, O_READY, O_FREE, kNumBars };
+enum FwdBar { Q_FULL, Q_EMPTY, K_FULL, K_EMPTY, V_FULL, V_EMPTY, S_READY, P_READY, O_READY, O_FREE, WORK_FULL0, WORK_FULL1,
+              WORK_EMPTY0, WORK_EMPTY1, kNumBars };
+
+// Attention weights of 32 consecutive keys of one query row, right to left, in groups of 8 keys.
+// With e = exp(s) and d = 1 + e:  beta = e / d,  1 - beta = 1 / d,  so for key m of a group entered with the carry W
+// (product of 1 - beta over everything to its right)
+//     p_m = beta_m * W * prod_{m' > m in group} 1/d_m'  =  e_m * (prod_{m' < m in group} d_m') * W / (prod over the group of d)
+// which needs one reciprocal per GROUP instead of one per key.  Scores are clamped at 2^15 (beta = 1 - 3e-5 there)
+// so that the product of 8 factors stays below 2^127.  Masked keys get e = 0: weight 0 and no stick broken.
+template <bool kMasked, bool kF16>
+__device__ __forceinline__ void fwd_chunk(uint32_t (&s)[32], float scale, int col0, int lim, float& W, uint32_t (&packed)[16]) {
+#pragma unroll
+    for (int g = 3; g >= 0; --g) {
+        float e[8], pre[8];
+        float run = 1.f;
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            float x = fminf(__uint_as_float(s[g * 8 + m]) * scale, 15.f);
+            e[m] = ex2_approx(x);
+            if (kMasked && col0 + g * 8 + m >= lim) e[m] = 0.f;
+            pre[m] = run;
+            run = fmaf(run, e[m], run);
+        }
+        const float f = W * rcp_approx(run);
+#pragma unroll
+        for (int m = 0; m < 8; ++m) s[g * 8 + m] = __float_as_uint(e[m] * pre[m] * f);
+        W = f;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) packed[j] = pack16<kF16>(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1]));
+}
 
 template <int D, bool kF16>
 __global__ void __launch_bounds__(kFwdThreads, 2)
@@ -46,6 +76,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     uint64_t* bars = (uint64_t*)(sV + kTileBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    SchedRing* ring = (SchedRing*)(tmem_slot + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -59,6 +90,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         mbar_init(&bars[P_READY], 128);
         mbar_init(&bars[O_READY], 1);
         mbar_init(&bars[O_FREE], 128);
+        mbar_init(&bars[WORK_FULL0], 1);
+        mbar_init(&bars[WORK_FULL1], 1);
+        mbar_init(&bars[WORK_EMPTY0], kRingConsumers);
+        mbar_init(&bars[WORK_EMPTY1], kRingConsumers);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -75,15 +110,18 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const int n_work = a.hdr->n_items * a.heads;
+    const int n_items = a.hdr->n_items;
+    const int n_work = n_items * a.heads;
 
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t ph_qe = 1, ph_ke = 1, ph_ve = 1;  // "empty" barriers start released
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
-                const Work wk = fetch_work(a, w);
+            SchedProducer sched;
+            int w;
+            while (ok && (w = sched.next(a.sched + 0, n_work, ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
+                const Work wk = fetch_work(a, n_items, w);
                 ok = mbar_wait(&bars[Q_EMPTY], ph_qe, abort_flag);
                 ph_qe ^= 1;
                 if (!ok) break;
@@ -130,8 +168,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 mma_commit(&bars[K_EMPTY]);
                 if (last_of_item) mma_commit(&bars[Q_EMPTY]);
             };
-            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
-                const Work wk = fetch_work(a, w);
+            SchedConsumer sched;
+            int w;
+            while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
+                const Work wk = fetch_work(a, n_items, w);
                 const int n_kt = wk.qt + 1;
                 ok = mbar_wait(&bars[Q_FULL], ph_qf, abort_flag);
                 ph_qf ^= 1;
@@ -176,8 +216,10 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const float scale = a.inv_temp * kLog2e;
         uint32_t ph_s = 0, ph_o = 0;
         bool ok = true;
-        for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
-            const Work wk = fetch_work(a, w);
+        SchedConsumer sched;
+        int w;
+        while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
+            const Work wk = fetch_work(a, n_items, w);
             const int qi = wk.qt * kBM + r;
             const bool row_ok = qi < wk.len;
             float* cw = a.carry_w ? a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r : nullptr;
@@ -188,30 +230,32 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 if (!ok) break;
                 tc_fence_after();
                 const bool diag = kt == wk.qt;
-                // keys of this tile visible from row r: columns < lim (all of them off the diagonal)
-                const int lim = diag ? (a.attend_current ? r + 1 : r) : kBN;
-#pragma unroll
-                for (int c = 3; c >= 0; --c) {
-                    if (cw && (c & 1)) cw[carry_slot(wk.slot_base, wk.qt, 2 * kt + (c >> 1)) * kTileQ] = W;
-                    uint32_t s[32];
-                    tmem_ld32(lane_base + kColS + c * 32, s);
-                    tmem_wait_ld();
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int j = 31; j >= 0; --j) {
-                        const float e = ex2_approx(__uint_as_float(s[j]) * scale);
-                        float om = rcp_approx(1.f + e);  // 1 - beta
-                        float beta = 1.f - om;
-                        if (c * 32 + j >= lim) { om = 1.f; beta = 0.f; }
-                        s[j] = __float_as_uint(beta * W);
-                        W *= om;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        packed[j] = kF16 ? pack_f16(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1]))
-                                         : pack_bf16(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1]));
-                    tmem_st16(lane_base + kColP + c * 16, packed);
-                }
+                // keys of the diagonal tile visible from row r: columns < lim
+                const int lim = a.attend_current ? r + 1 : r;
+                // chunks of 32 columns, right to left; the load of the next chunk is in flight while one is computed
+                uint32_t sa[32], sb[32], packed[16];
+                tmem_ld32(lane_base + kColS + 96, sa);
+                tmem_wait_ld();
+                tmem_ld32(lane_base + kColS + 64, sb);
+                if (cw) cw[carry_slot(wk.slot_base, wk.qt, 2 * kt + 1) * kTileQ] = W;
+                if (diag) fwd_chunk<true, kF16>(sa, scale, 96, lim, W, packed);
+                else fwd_chunk<false, kF16>(sa, scale, 96, lim, W, packed);
+                tmem_st16(lane_base + kColP + 48, packed);
+                tmem_wait_ld();
+                tmem_ld32(lane_base + kColS + 32, sa);
+                if (diag) fwd_chunk<true, kF16>(sb, scale, 64, lim, W, packed);
+                else fwd_chunk<false, kF16>(sb, scale, 64, lim, W, packed);
+                tmem_st16(lane_base + kColP + 32, packed);
+                tmem_wait_ld();
+                tmem_ld32(lane_base + kColS + 0, sb);
+                if (cw) cw[carry_slot(wk.slot_base, wk.qt, 2 * kt) * kTileQ] = W;
+                if (diag) fwd_chunk<true, kF16>(sa, scale, 32, lim, W, packed);
+                else fwd_chunk<false, kF16>(sa, scale, 32, lim, W, packed);
+                tmem_st16(lane_base + kColP + 16, packed);
+                tmem_wait_ld();
+                if (diag) fwd_chunk<true, kF16>(sb, scale, 0, lim, W, packed);
+                else fwd_chunk<false, kF16>(sb, scale, 0, lim, W, packed);
+                tmem_st16(lane_base + kColP + 0, packed);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars[P_READY]);
@@ -234,10 +278,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         uint4 u;
                         uint32_t* up = (uint32_t*)&u;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float lo = __uint_as_float(v[g * 8 + 2 * j]), hi = __uint_as_float(v[g * 8 + 2 * j + 1]);
-                            up[j] = kF16 ? pack_f16(lo, hi) : pack_bf16(lo, hi);
-                        }
+                        for (int j = 0; j < 4; ++j)
+                            up[j] = pack16<kF16>(__uint_as_float(v[g * 8 + 2 * j]), __uint_as_float(v[g * 8 + 2 * j + 1]));
                         *(uint4*)(orow + (c * 32 + g * 8) * 2) = u;
                     }
                 }
@@ -254,6 +296,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
     }
     tc_teardown(abort_flag, a.status, tmem, kTmemCols, 5);
+    sched_finish(a.sched + 0);
 }
 
 template <int D, bool kF16>
@@ -266,7 +309,7 @@ int launch_fwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         encode_tile_map(&mv, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBN))
         return 1;
     // at least 80 KB so that never more than two blocks (2 x 256 TMEM columns) share an SM
-    constexpr int smem = (3 * kBM * D * 2 + 1024 + 256) > 81920 ? (3 * kBM * D * 2 + 1024 + 256) : 81920;
+    constexpr int smem = (3 * kBM * D * 2 + 1024 + 512) > 81920 ? (3 * kBM * D * 2 + 1024 + 512) : 81920;
     cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     cudaFuncSetAttribute(tc_fwd_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
