@@ -1,22 +1,27 @@
 // Tensor-core forward (sm_100a): o, rem, neg_log_acc and the per-64-key carries of W for bf16 / f16 inputs with
 // head_dim 64 or 128.
 //
-// One work item = (head, sequence, 128-row query tile).  A persistent grid of 2 thread blocks per SM walks the
-// item table built by the prep kernel (heaviest items first, round-robin over the blocks).  Per item the key tiles
-// are visited right to left, from the diagonal to key 0 -- the order of the reference's _forward_one_row
+// One work item = (head, sequence, 128-row query tile); one persistent thread block per SM draws items from a global
+// counter (heaviest first, interleaved over small groups of heads so that their K and V stay in L2).  Per item the key
+// tiles are visited right to left, from the diagonal to key 0 -- the order of the reference's _forward_one_row
 // (stickbreaking_attention/sb_varlen/sb_varlen_fwd.py:155-193) -- because the weight of key j needs the product of
 // (1 - beta) over the keys to its right.
 //
-// Roles inside a block (192 threads):
-//   warps 0-3  one thread per query row: reads the 128 scores of its row from tensor memory, turns them into
-//              attention weights in fp32 registers (beta = sigmoid(s), running product W of 1 - beta, p = beta * W),
-//              writes them back to tensor memory as 16-bit operands; epilogue: o, rem, neg_log_acc to global memory.
-//   warp 4     TMA producer: Q once per item, then K and V tiles (single stage each; K of tile t+1 arrives while
-//              the weights of tile t are computed, V of tile t+1 while S of t+1 is computed).
-//   warp 5     issues tcgen05.mma: S = Q K^T (both operands in shared memory) into TMEM columns [0,128),
-//              O += P V (P from TMEM columns [64,128), V from shared memory) into columns [128,128+D).
-// P overwrites the right half of S: a row is processed right to left in chunks of 32 columns and the packed
-// weights of chunk c land in columns that were already read.
+// Warps of a block (352 threads):
+//   0-3 / 4-7  row group 0 / 1, one thread per query row in each.  The groups take the key tiles of an item in turn
+//              (group 0 the 1st, 3rd, ... tile from the diagonal, group 1 the others).  S lives in three rotating
+//              buffers in tensor memory, so the tensor cores are always two tiles ahead: while the groups turn
+//              scores into weights on the CUDA cores, S of later tiles and O += P V of earlier ones are in flight.
+//              A thread reads the 128 scores of its row, computes the weights RELATIVE to a carry of 1, receives the
+//              true carry W (product of 1 - beta over everything to the right of the tile) from its partner thread
+//              in the other group through shared memory, passes its own on, rescales, and writes the weights back to
+//              tensor memory as 16-bit operands.
+//   8 / 10     TMA producers: warp 8 loads Q once per item and the K tiles (three-stage ring, S runs ahead), warp 10
+//              the V tiles (two-stage ring).
+//   9          issues tcgen05.mma: S = Q K^T (both operands in shared memory) into the next S buffer of the rotation,
+//              O += P V (P from tensor memory, V from shared memory).
+// Tensor memory (512 columns): S buffers at columns 0, 128, 256; O [384,384+D).  P overwrites the right half of its S
+// buffer after the whole row has been read.
 #include "sb_tc_common.cuh"
 
 namespace sb {
@@ -25,44 +30,57 @@ using namespace sm100;
 
 namespace {
 
-constexpr int kFwdThreads = 192;
+constexpr int kFwdThreads = 352;
 constexpr int kBM = 128, kBN = 128;
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColP = 64, kColO = 128;
-enum FwdBar { Q_FULL, Q_EMPTY, K_FULL, K_EMPTY, V_FULL, V_EMPTY, S_READY, P_READY, O_READY, O_FREE, WORK_FULL0, WORK_FULL1,
-              WORK_EMPTY0, WORK_EMPTY1, kNumBars };
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS0 = 0, kColO = 384, kColPOff = 64;  // S buffer i at 128*i (i = step mod 3), its P at +64
+constexpr int kKStages = 3, kVStages = 2;
+enum FwdBar { Q_FULL, Q_EMPTY, K_FULL0, K_FULL1, K_FULL2, K_EMPTY0, K_EMPTY1, K_EMPTY2, V_FULL0, V_FULL1, V_EMPTY0, V_EMPTY1, S_READY0, S_READY1,
+              S_READY2, P_READY0, P_READY1, P_READY2, X_W0, X_W1, O_READY, O_FREE, WORK_FULL0, WORK_FULL1, WORK_EMPTY0, WORK_EMPTY1, kNumBars };
 
-// Attention weights of 32 consecutive keys of one query row, right to left, in groups of 8 keys.
-// With e = exp(s) and d = 1 + e:  beta = e / d,  1 - beta = 1 / d,  so for key m of a group entered with the carry W
-// (product of 1 - beta over everything to its right)
+// With e = exp(s) and d = 1 + e:  beta = e / d,  1 - beta = 1 / d.  For key m of a group of 8 keys entered with the
+// carry W (product of 1 - beta over everything to its right)
 //     p_m = beta_m * W * prod_{m' > m in group} 1/d_m'  =  e_m * (prod_{m' < m in group} d_m') * W / (prod over the group of d)
 // which needs one reciprocal per GROUP instead of one per key.  Scores are clamped at 2^15 (beta = 1 - 3e-5 there)
 // so that the product of 8 factors stays below 2^127.  Masked keys get e = 0: weight 0 and no stick broken.
-template <bool kMasked, bool kF16>
-__device__ __forceinline__ void fwd_chunk(uint32_t (&s)[32], float scale, int col0, int lim, float& W, uint32_t (&packed)[16]) {
+//
+// First pass over a chunk of 32 keys: s[idx] <- e * (product of d over the keys of its group to the LEFT);
+// run[g] <- product of d over group g.  The four groups are swept side by side so that their chains overlap.
+template <bool kMasked>
+__device__ __forceinline__ void fwd_sweep(uint32_t (&s)[32], float scale, int col0, int lim, float (&run)[4]) {
 #pragma unroll
-    for (int g = 3; g >= 0; --g) {
-        float e[8], pre[8];
-        float run = 1.f;
+    for (int g = 0; g < 4; ++g) run[g] = 1.f;
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            float x = fminf(__uint_as_float(s[g * 8 + m]) * scale, 15.f);
-            e[m] = ex2_approx(x);
-            if (kMasked && col0 + g * 8 + m >= lim) e[m] = 0.f;
-            pre[m] = run;
-            run = fmaf(run, e[m], run);
+    for (int m = 0; m < 8; ++m) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const int idx = g * 8 + m;
+            float e = ex2_approx(fminf(__uint_as_float(s[idx]) * scale, 15.f));
+            if (kMasked && col0 + idx >= lim) e = 0.f;
+            s[idx] = __float_as_uint(e * run[g]);
+            run[g] = fmaf(run[g], e, run[g]);
         }
-        const float f = W * rcp_approx(run);
-#pragma unroll
-        for (int m = 0; m < 8; ++m) s[g * 8 + m] = __float_as_uint(e[m] * pre[m] * f);
-        W = f;
     }
+}
+// carry entering each group from the right: f[g] = W / (product of d over groups g..3); W <- the chunk's exit carry
+__device__ __forceinline__ void fwd_carries(const float (&run)[4], float& W, float* f) {
+    f[3] = W * rcp_approx(run[3]);
+    f[2] = f[3] * rcp_approx(run[2]);
+    f[1] = f[2] * rcp_approx(run[1]);
+    f[0] = f[1] * rcp_approx(run[0]);
+    W = f[0];
+}
+template <bool kF16>
+__device__ __forceinline__ void fwd_finish(const uint32_t (&s)[32], const float* f, float mul, uint32_t (&packed)[16]) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) packed[j] = pack16<kF16>(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1]));
+    for (int j = 0; j < 16; ++j) {
+        const float fj = f[j >> 2] * mul;
+        packed[j] = pack16<kF16>(__uint_as_float(s[2 * j]) * fj, __uint_as_float(s[2 * j + 1]) * fj);
+    }
 }
 
 template <int D, bool kF16>
-__global__ void __launch_bounds__(kFwdThreads, 2)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const KArgs a) {
     constexpr int kTileBytes = kBM * D * 2;
@@ -71,37 +89,31 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + kTileBytes;
-    uint8_t* sV = sK + kTileBytes;
-    uint64_t* bars = (uint64_t*)(sV + kTileBytes);
-    uint32_t* tmem_slot = (uint32_t*)(bars + kNumBars);
+    uint8_t* sK = sQ + kTileBytes;             // kKStages tiles
+    uint8_t* sV = sK + kKStages * kTileBytes;  // kVStages tiles
+    uint64_t* bars = (uint64_t*)(sV + kVStages * kTileBytes);
+    SchedRing* ring = (SchedRing*)(bars + kNumBars);
+    uint32_t* tmem_slot = (uint32_t*)(ring + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    SchedRing* ring = (SchedRing*)(tmem_slot + 2);
+    float* xw = (float*)(tmem_slot + 4);  // [group][128 rows]: carry leaving the tile the group has just swept
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        mbar_init(&bars[Q_FULL], 1);
-        mbar_init(&bars[Q_EMPTY], 1);
-        mbar_init(&bars[K_FULL], 1);
-        mbar_init(&bars[K_EMPTY], 1);
-        mbar_init(&bars[V_FULL], 1);
-        mbar_init(&bars[V_EMPTY], 1);
-        mbar_init(&bars[S_READY], 1);
-        mbar_init(&bars[P_READY], 128);
-        mbar_init(&bars[O_READY], 1);
-        mbar_init(&bars[O_FREE], 128);
-        mbar_init(&bars[WORK_FULL0], 1);
-        mbar_init(&bars[WORK_FULL1], 1);
-        mbar_init(&bars[WORK_EMPTY0], kRingConsumers);
-        mbar_init(&bars[WORK_EMPTY1], kRingConsumers);
+        for (int i = 0; i < kNumBars; ++i) {
+            uint32_t cnt = 1;
+            if (i == P_READY0 || i == P_READY1 || i == P_READY2 || i == X_W0 || i == X_W1) cnt = 128;
+            if (i == O_FREE) cnt = 256;
+            if (i == WORK_EMPTY0 || i == WORK_EMPTY1) cnt = 258;  // MMA thread, V producer, 256 row threads
+            mbar_init(&bars[i], cnt);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == 8 && lane == 0) {
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
@@ -113,10 +125,11 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const int n_items = a.hdr->n_items;
     const int n_work = n_items * a.heads;
 
-    if (warp == 4) {
-        // ------------------------------------------------------------------ TMA producer
+    if (warp == 8) {
+        // ------------------------------------------------------------------ TMA producer: Q and K
         if (lane == 0) {
-            uint32_t ph_qe = 1, ph_ke = 1, ph_ve = 1;  // "empty" barriers start released
+            uint32_t ph_qe = 1, ph_ke = 7;  // "empty" barriers start released; bit i of ph_ke: K stage i
+            uint32_t st = 0;                // K stage of the next tile
             bool ok = true;
             SchedProducer sched;
             int w;
@@ -130,147 +143,219 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 for (int bx = 0; bx < kBoxes; ++bx)
                     tma_load_4d(sQ + bx * kBoxBytes, &map_q, &bars[Q_FULL], bx * 64, wk.start + wk.qt * kBM, wk.h, wk.b);
                 for (int kt = wk.qt; kt >= 0; --kt) {
-                    const int row = wk.start + kt * kBN;
-                    ok = mbar_wait(&bars[K_EMPTY], ph_ke, abort_flag);
-                    ph_ke ^= 1;
+                    ok = mbar_wait(&bars[K_EMPTY0 + st], (ph_ke >> st) & 1, abort_flag);
+                    ph_ke ^= 1u << st;
                     if (!ok) break;
-                    mbar_expect_tx(&bars[K_FULL], kTileBytes);
+                    mbar_expect_tx(&bars[K_FULL0 + st], kTileBytes);
 #pragma unroll
                     for (int bx = 0; bx < kBoxes; ++bx)
-                        tma_load_4d(sK + bx * kBoxBytes, &map_k, &bars[K_FULL], bx * 64, row, wk.h, wk.b);
-                    ok = mbar_wait(&bars[V_EMPTY], ph_ve, abort_flag);
-                    ph_ve ^= 1;
-                    if (!ok) break;
-                    mbar_expect_tx(&bars[V_FULL], kTileBytes);
-#pragma unroll
-                    for (int bx = 0; bx < kBoxes; ++bx)
-                        tma_load_4d(sV + bx * kBoxBytes, &map_v, &bars[V_FULL], bx * 64, row, wk.h, wk.b);
+                        tma_load_4d(sK + st * kTileBytes + bx * kBoxBytes, &map_k, &bars[K_FULL0 + st], bx * 64,
+                                    wk.start + kt * kBN, wk.h, wk.b);
+                    st = st == kKStages - 1 ? 0 : st + 1;
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 10) {
+        // ------------------------------------------------------------------ TMA producer: V
+        if (lane == 0) {
+            uint32_t ph_ve0 = 1, ph_ve1 = 1;
+            uint32_t kv = 0;
+            bool ok = true;
+            SchedConsumer sched;
+            int w;
+            while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
+                const Work wk = fetch_work(a, n_items, w);
+                for (int kt = wk.qt; kt >= 0; --kt, ++kv) {
+                    const int st = kv & 1;
+                    uint32_t& ph_ve = st ? ph_ve1 : ph_ve0;
+                    ok = mbar_wait(&bars[V_EMPTY0 + st], ph_ve, abort_flag);
+                    ph_ve ^= 1;
+                    if (!ok) break;
+                    mbar_expect_tx(&bars[V_FULL0 + st], kTileBytes);
+#pragma unroll
+                    for (int bx = 0; bx < kBoxes; ++bx)
+                        tma_load_4d(sV + st * kTileBytes + bx * kBoxBytes, &map_v, &bars[V_FULL0 + st], bx * 64,
+                                    wk.start + kt * kBN, wk.h, wk.b);
+                }
+            }
+        }
+    } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_s = make_idesc(kBM, kBN, kF16 ? 0 : 1, 0, 0);
             constexpr uint32_t idesc_o = make_idesc(kBM, D, kF16 ? 0 : 1, 0, 1);
             const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            uint32_t ph_qf = 0, ph_kf = 0, ph_vf = 0, ph_p = 0, ph_of = 1;
+            uint32_t ph_qf = 0, ph_kf = 0, ph_vf0 = 0, ph_vf1 = 0, ph_of = 1;  // bit i of ph_kf: K stage i
+            uint32_t ph_p = 0;   // bit i: parity of P_READY of S buffer i
+            uint32_t sbuf = 0;   // running step count modulo 3 = S buffer of the next S to issue
+            uint32_t pbuf = 0;   // S buffer of the next P to consume
+            uint32_t ks = 0, vs = 0;  // K stage of the next S; running count of V tiles consumed by P V
             bool ok = true;
-            auto issue_s = [&](bool last_of_item) {
+            SB_TRACE_DECL(m);
+            // S of step j of the current item into the next S buffer of the rotation
+            auto issue_s = [&](int j, int n) {
+                const uint32_t st = ks;
+                ks = ks == kKStages - 1 ? 0 : ks + 1;
+                ok = mbar_wait(&bars[K_FULL0 + st], (ph_kf >> st) & 1, abort_flag);
+                ph_kf ^= 1u << st;
+                if (!ok) return;
                 tc_fence_after();
+                const uint32_t kk = k_addr + st * kTileBytes;
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
                     const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-                    mma_ss(tmem + kColS, make_smem_desc(q_addr + off, 0, 1024), make_smem_desc(k_addr + off, 0, 1024),
-                           idesc_s, k > 0);
+                    mma_ss(tmem + kColS0 + 128 * sbuf, make_smem_desc(q_addr + off, 0, 1024),
+                           make_smem_desc(kk + off, 0, 1024), idesc_s, k > 0);
                 }
-                mma_commit(&bars[S_READY]);
-                mma_commit(&bars[K_EMPTY]);
-                if (last_of_item) mma_commit(&bars[Q_EMPTY]);
+                mma_commit(&bars[S_READY0 + sbuf]);
+                sbuf = sbuf == 2 ? 0 : sbuf + 1;
+                mma_commit(&bars[K_EMPTY0 + st]);
+                if (j == n - 1) mma_commit(&bars[Q_EMPTY]);
             };
             SchedConsumer sched;
             int w;
             while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
                 const Work wk = fetch_work(a, n_items, w);
-                const int n_kt = wk.qt + 1;
+                const int n = wk.qt + 1;
                 ok = mbar_wait(&bars[Q_FULL], ph_qf, abort_flag);
                 ph_qf ^= 1;
                 if (!ok) break;
-                ok = mbar_wait(&bars[K_FULL], ph_kf, abort_flag);
-                ph_kf ^= 1;
-                if (!ok) break;
-                issue_s(n_kt == 1);
-                for (int t = 0; t < n_kt; ++t) {
-                    ok = mbar_wait(&bars[P_READY], ph_p, abort_flag);
-                    ph_p ^= 1;
+                issue_s(0, n);
+                if (ok && n > 1) issue_s(1, n);
+                if (ok && n > 2) issue_s(2, n);
+                for (int j = 0; ok && j < n; ++j) {
+                    const uint32_t b = pbuf;
+                    pbuf = pbuf == 2 ? 0 : pbuf + 1;
+                    SB_TRACE_EV(m, 0, 1);
+                    ok = mbar_wait(&bars[P_READY0 + b], (ph_p >> b) & 1, abort_flag);
+                    ph_p ^= 1u << b;
                     if (!ok) break;
-                    ok = mbar_wait(&bars[V_FULL], ph_vf, abort_flag);
+                    SB_TRACE_EV(m, 0, 2);
+                    const int st = vs & 1;
+                    ++vs;
+                    uint32_t& ph_vf = st ? ph_vf1 : ph_vf0;
+                    ok = mbar_wait(&bars[V_FULL0 + st], ph_vf, abort_flag);
                     ph_vf ^= 1;
                     if (!ok) break;
-                    if (t == 0) {  // the previous item's O must have been read out
+                    if (j == 0) {  // the previous item's O must have been read out
                         ok = mbar_wait(&bars[O_FREE], ph_of, abort_flag);
                         ph_of ^= 1;
                         if (!ok) break;
                     }
                     tc_fence_after();
+                    const uint32_t vv = v_addr + st * kTileBytes;
 #pragma unroll
                     for (int k = 0; k < kBN / 16; ++k)
-                        mma_ts(tmem + kColO, tmem + kColP + k * 8, make_smem_desc(v_addr + k * 2048, kBoxBytes, 1024),
-                               idesc_o, (t > 0 || k > 0) ? 1u : 0u);
-                    mma_commit(&bars[V_EMPTY]);
-                    if (t + 1 < n_kt) {
-                        ok = mbar_wait(&bars[K_FULL], ph_kf, abort_flag);
-                        ph_kf ^= 1;
-                        if (!ok) break;
-                        issue_s(t + 2 == n_kt);
-                    } else {
-                        mma_commit(&bars[O_READY]);
-                    }
+                        mma_ts(tmem + kColO, tmem + kColS0 + 128 * b + kColPOff + k * 8,
+                               make_smem_desc(vv + k * 2048, kBoxBytes, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    mma_commit(&bars[V_EMPTY0 + st]);
+                    SB_TRACE_EV(m, 0, 3);
+                    if (j + 3 < n) issue_s(j + 3, n);
+                    SB_TRACE_EV(m, 0, 4);
                 }
+                if (!ok) break;
+                mma_commit(&bars[O_READY]);
             }
         }
     } else {
-        // ------------------------------------------------------------------ one thread per query row
-        const int r = tid;  // row of the tile == TMEM lane
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        // ------------------------------------------------------------------ row groups
+        const int b = warp >> 2;               // group
+        const int r = (warp & 3) * 32 + lane;  // row of the tile == TMEM lane
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        uint32_t step = 0;   // key tiles of all items so far: tile number g uses S buffer g % 3 for the (g / 3)-th time
         const float scale = a.inv_temp * kLog2e;
-        uint32_t ph_s = 0, ph_o = 0;
+        float* x_mine = xw + b * 128;
+        const float* x_other = xw + (b ^ 1) * 128;
+        uint32_t ph_o = 0, ph_x = 0;
         bool ok = true;
+        SB_TRACE_DECL(c);
         SchedConsumer sched;
         int w;
         while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
             const Work wk = fetch_work(a, n_items, w);
+            const int n = wk.qt + 1;
             const int qi = wk.qt * kBM + r;
             const bool row_ok = qi < wk.len;
             float* cw = a.carry_w ? a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r : nullptr;
-            float W = 1.f;
-            for (int kt = wk.qt; kt >= 0; --kt) {
-                ok = mbar_wait(&bars[S_READY], ph_s, abort_flag);
-                ph_s ^= 1;
+            const int lim = a.attend_current ? r + 1 : r;  // diagonal tile: columns < lim are visible
+            float W = 1.f;  // carry leaving the last tile this thread swept
+            for (int j = b; j < n; j += 2) {
+                const int kt = wk.qt - j;
+                const uint32_t g = step + j, sb = g % 3;
+                const uint32_t s_base = lane_base + kColS0 + 128 * sb;
+                if (r == 0) SB_TRACE_EV(c, 1 + b, 1);
+                // both groups wait on the barriers of a buffer in turn: the parity follows from the use count
+                ok = mbar_wait(&bars[S_READY0 + sb], (g / 3) & 1, abort_flag);
                 if (!ok) break;
+                if (r == 0) SB_TRACE_EV(c, 1 + b, 2);
                 tc_fence_after();
-                const bool diag = kt == wk.qt;
-                // keys of the diagonal tile visible from row r: columns < lim
-                const int lim = a.attend_current ? r + 1 : r;
-                // chunks of 32 columns, right to left; the load of the next chunk is in flight while one is computed
-                uint32_t sa[32], sb[32], packed[16];
-                tmem_ld32(lane_base + kColS + 96, sa);
+                // sweep the row right to left relative to an entering carry of 1
+                uint32_t u3[32], u2[32], u1[32], u0[32], packed[16];
+                float run[4], f[16];
+                float Wl = 1.f;
+                tmem_ld32(s_base + 96, u3);
+                tmem_ld32(s_base + 64, u2);
                 tmem_wait_ld();
-                tmem_ld32(lane_base + kColS + 64, sb);
-                if (cw) cw[carry_slot(wk.slot_base, wk.qt, 2 * kt + 1) * kTileQ] = W;
-                if (diag) fwd_chunk<true, kF16>(sa, scale, 96, lim, W, packed);
-                else fwd_chunk<false, kF16>(sa, scale, 96, lim, W, packed);
-                tmem_st16(lane_base + kColP + 48, packed);
-                tmem_wait_ld();
-                tmem_ld32(lane_base + kColS + 32, sa);
-                if (diag) fwd_chunk<true, kF16>(sb, scale, 64, lim, W, packed);
-                else fwd_chunk<false, kF16>(sb, scale, 64, lim, W, packed);
-                tmem_st16(lane_base + kColP + 32, packed);
-                tmem_wait_ld();
-                tmem_ld32(lane_base + kColS + 0, sb);
-                if (cw) cw[carry_slot(wk.slot_base, wk.qt, 2 * kt) * kTileQ] = W;
-                if (diag) fwd_chunk<true, kF16>(sa, scale, 32, lim, W, packed);
-                else fwd_chunk<false, kF16>(sa, scale, 32, lim, W, packed);
-                tmem_st16(lane_base + kColP + 16, packed);
-                tmem_wait_ld();
-                if (diag) fwd_chunk<true, kF16>(sb, scale, 0, lim, W, packed);
-                else fwd_chunk<false, kF16>(sb, scale, 0, lim, W, packed);
-                tmem_st16(lane_base + kColP + 0, packed);
+                tmem_ld32(s_base + 32, u1);
+                tmem_ld32(s_base + 0, u0);
+                if (j == 0) {
+                    fwd_sweep<true>(u3, scale, 96, lim, run); fwd_carries(run, Wl, f + 12);
+                    fwd_sweep<true>(u2, scale, 64, lim, run); fwd_carries(run, Wl, f + 8);
+                    tmem_wait_ld();
+                    fwd_sweep<true>(u1, scale, 32, lim, run); fwd_carries(run, Wl, f + 4);
+                    fwd_sweep<true>(u0, scale, 0, lim, run); fwd_carries(run, Wl, f + 0);
+                } else {
+                    fwd_sweep<false>(u3, scale, 96, lim, run); fwd_carries(run, Wl, f + 12);
+                    fwd_sweep<false>(u2, scale, 64, lim, run); fwd_carries(run, Wl, f + 8);
+                    tmem_wait_ld();
+                    fwd_sweep<false>(u1, scale, 32, lim, run); fwd_carries(run, Wl, f + 4);
+                    fwd_sweep<false>(u0, scale, 0, lim, run); fwd_carries(run, Wl, f + 0);
+                }
+                if (r == 0) SB_TRACE_EV(c, 1 + b, 3);
+                // the true entering carry comes from the partner thread, which swept the tile to the right
+                float Win = 1.f;
+                if (j > 0) {
+                    ok = mbar_wait(&bars[X_W0 + (b ^ 1)], ph_x, abort_flag);
+                    ph_x ^= 1;
+                    if (!ok) break;
+                    Win = x_other[r];
+                }
+                W = Win * Wl;
+                if (j + 1 < n) {
+                    x_mine[r] = W;
+                    mbar_arrive(&bars[X_W0 + b]);
+                }
+                if (r == 0) SB_TRACE_EV(c, 1 + b, 4);
+                if (cw) {
+                    cw[carry_slot(wk.slot_base, wk.qt, 2 * kt + 1) * kTileQ] = Win;
+                    cw[carry_slot(wk.slot_base, wk.qt, 2 * kt) * kTileQ] = Win * f[8];
+                }
+                fwd_finish<kF16>(u3, f + 12, Win, packed);
+                tmem_st16(s_base + kColPOff + 48, packed);
+                fwd_finish<kF16>(u2, f + 8, Win, packed);
+                tmem_st16(s_base + kColPOff + 32, packed);
+                fwd_finish<kF16>(u1, f + 4, Win, packed);
+                tmem_st16(s_base + kColPOff + 16, packed);
+                fwd_finish<kF16>(u0, f + 0, Win, packed);
+                tmem_st16(s_base + kColPOff + 0, packed);
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(&bars[P_READY]);
+                mbar_arrive(&bars[P_READY0 + sb]);
+                if (r == 0) SB_TRACE_EV(c, 1 + b, 5);
             }
             if (!ok) break;
-            // epilogue
+            step += n;
+            // epilogue: each group stores half of the head dim of every row
             ok = mbar_wait(&bars[O_READY], ph_o, abort_flag);
             ph_o ^= 1;
             if (!ok) break;
             tc_fence_after();
-            char* orow = a.o.ptr + 2 * ((int64_t)wk.b * a.o.sb + (int64_t)wk.h * a.o.sh + (int64_t)(wk.start + qi) * a.o.st);
+            const int d0 = b * (D / 2);
+            char* orow = a.o.ptr + 2 * ((int64_t)wk.b * a.o.sb + (int64_t)wk.h * a.o.sh + (int64_t)(wk.start + qi) * a.o.st + d0);
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < D / 64; ++c) {
                 uint32_t v[32];
-                tmem_ld32(lane_base + kColO + c * 32, v);
+                tmem_ld32(lane_base + kColO + d0 + c * 32, v);
                 tmem_wait_ld();
                 if (row_ok) {
 #pragma unroll
@@ -278,15 +363,15 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         uint4 u;
                         uint32_t* up = (uint32_t*)&u;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            up[j] = pack16<kF16>(__uint_as_float(v[g * 8 + 2 * j]), __uint_as_float(v[g * 8 + 2 * j + 1]));
+                        for (int jj = 0; jj < 4; ++jj)
+                            up[jj] = pack16<kF16>(__uint_as_float(v[g * 8 + 2 * jj]), __uint_as_float(v[g * 8 + 2 * jj + 1]));
                         *(uint4*)(orow + (c * 32 + g * 8) * 2) = u;
                     }
                 }
             }
             tc_fence_before();
             mbar_arrive(&bars[O_FREE]);
-            if (row_ok) {
+            if (row_ok && ((n - 1) & 1) == b) {  // this group swept the leftmost tile: W is the remainder of the row
                 const int64_t t = wk.start + qi;
                 char* rp = a.rem.ptr + 2 * ((int64_t)wk.b * a.rem.sb + (int64_t)wk.h * a.rem.sh + t * a.rem.st);
                 if (kF16) *(__half*)rp = __float2half_rn(W);
@@ -295,7 +380,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             }
         }
     }
-    tc_teardown(abort_flag, a.status, tmem, kTmemCols, 5);
+    tc_teardown(abort_flag, a.status, tmem, kTmemCols, 9);
     sched_finish(a.sched + 0);
 }
 
@@ -308,12 +393,12 @@ int launch_fwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         encode_tile_map(&mk, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBN) ||
         encode_tile_map(&mv, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBN))
         return 1;
-    // at least 80 KB so that never more than two blocks (2 x 256 TMEM columns) share an SM
-    constexpr int smem = (3 * kBM * D * 2 + 1024 + 512) > 81920 ? (3 * kBM * D * 2 + 1024 + 512) : 81920;
+    // Q + three K stages + two V stages; at least 120 KB so that one block owns the SM and its tensor memory
+    constexpr int need = (1 + kKStages + kVStages) * kBM * D * 2 + 1024 + 2048;
+    constexpr int smem = need > 120 * 1024 ? need : 120 * 1024;
     cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    cudaFuncSetAttribute(tc_fwd_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    tc_fwd_kernel<D, kF16><<<2 * sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
+    tc_fwd_kernel<D, kF16><<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
     return (int)cudaGetLastError();
 }
 
