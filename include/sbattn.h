@@ -36,6 +36,7 @@ extern "C" {
 #define SBATTN_EWORKSPACE (-4)   /* workspace missing or smaller than sbattn_workspace_bytes says        */
 #define SBATTN_EALIGN (-5)       /* tensor-core path asked for, but pointers/strides are not 16-B aligned */
 #define SBATTN_ECUDA (-6)        /* a CUDA runtime/driver call failed (launch error, no sm_100 device)   */
+#define SBATTN_ECAPACITY (-7)    /* sbattn_fwd_static: the problem needs more than the built-in scratch  */
 
 /* bits of the device status word (0 = fine) */
 #define SBATTN_ST_BAD_SEQLENS 1u /* sequence ends decrease, exceed the token count or max_seqlen         */
@@ -115,6 +116,25 @@ int sbattn_fwd(const SbParams* p);
 /* dq, dk, dv <- do, drem, q, k, v and the forward's workspace.
  * Replaces varlen_bwd (sb_varlen_bwd.py:483) and _bwd (sb_bwd.py:162). */
 int sbattn_bwd(const SbParams* p);
+
+/* Forward without any allocation by anybody: the tables the forward needs live in a fixed 1 MiB array inside the
+ * library (sbattn_static_scratch_bytes), which every GPU that loads the library holds until the process exits.
+ * It has no counterpart in the reference.  It exists for callers that cannot allocate device memory at the call:
+ * an inference server whose memory pool owns the whole device, a plugin that must not touch its host's allocator.
+ *   - p->fwd_workspace, p->save_carries are ignored; no backward can follow (gradient-free forward only).  The caller
+ *     still passes q, k, v, o, rem, neg_log_acc, cu_seqlens and the status word.
+ *   - Returns SBATTN_ECAPACITY when the work-item tables of the shape do not fit (they need roughly
+ *     16 bytes per sequence + 8 bytes per 128 tokens: a million tokens in tens of thousands of sequences fit).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress) with that device
+ *     current; make that first call outside any stream capture.  Later calls only launch kernels.
+ *   - All calls on one GPU share the array.  Every call rewrites the tables and zeroes its counters itself, so
+ *     calls that follow each other on one stream are safe; calls that can overlap on the GPU (different streams,
+ *     different threads) race on it and must be serialised by the caller.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine. */
+int sbattn_fwd_static(const SbParams* p);
+
+/* Size in bytes of the built-in scratch of sbattn_fwd_static.  No counterpart in the reference. */
+size_t sbattn_static_scratch_bytes(void);
 
 /* Text for a return code.  No counterpart in the reference (it raises Python exceptions). */
 const char* sbattn_strerror(int code);

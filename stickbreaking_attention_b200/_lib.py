@@ -37,7 +37,7 @@ class SbParams(ctypes.Structure):
 
 
 EXPORTS = ("sbattn_workspace_bytes", "sbattn_fwd", "sbattn_bwd", "sbattn_strerror", "sbattn_version",
-           "sbattn_params_size")
+           "sbattn_params_size", "sbattn_fwd_static", "sbattn_static_scratch_bytes")
 
 _lib = None
 
@@ -69,6 +69,9 @@ def lib():
         L.sbattn_strerror.restype = ctypes.c_char_p
         L.sbattn_version.restype = ctypes.c_int
         L.sbattn_params_size.restype = ctypes.c_size_t
+        L.sbattn_fwd_static.argtypes = [ctypes.POINTER(SbParams)]
+        L.sbattn_fwd_static.restype = ctypes.c_int
+        L.sbattn_static_scratch_bytes.restype = ctypes.c_size_t
         if L.sbattn_params_size() != ctypes.sizeof(SbParams):
             raise RuntimeError("libsbattn.so and its Python binding disagree about SbParams")
         _lib = L

@@ -92,6 +92,7 @@ extern "C" const char* sbattn_strerror(int code) {
         case SBATTN_EWORKSPACE: return "workspace missing or too small";
         case SBATTN_EALIGN: return "tensor-core path needs 16-byte aligned pointers and strides";
         case SBATTN_ECUDA: return "CUDA call failed";
+        case SBATTN_ECAPACITY: return "problem too large for the built-in scratch of sbattn_fwd_static";
         default: return "unknown sbattn error";
     }
 }
