@@ -207,6 +207,30 @@ def run_reference(args, wl):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------ sharding
+def shard_of(wl, world, rank):
+    """What rank `rank` of `world` processes works on: (heads of its batch, first head, whole batches in the job).
+
+    Every (head, sequence) pair is independent, so there is no collective on the data path.  Default workloads give
+    every rank a whole batch of its own (weak scaling: `world` batches in the job); a workload with `split_heads`
+    is ONE batch whose heads are cut into `world` contiguous slices (strong scaling)."""
+    H = wl["H"]
+    if wl["split_heads"]:
+        if H % world:
+            raise SystemExit("heads must divide over the ranks")
+        return H // world, rank * (H // world), 1
+    return H, 0, world
+
+
+def max_over_ranks(ms, world, device):
+    """Device time of the job = the slowest rank's."""
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 # ------------------------------------------------------------------------------------------------ GPU arm
 def run_ours(args, wl):
     import torch.distributed as dist
@@ -222,11 +246,8 @@ def run_ours(args, wl):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    H, D, lengths = wl["H"], wl["D"], wl["lengths"]
-    if wl["split_heads"]:
-        if H % world:
-            raise SystemExit("heads must divide over the ranks")
-        H = H // world
+    D, lengths = wl["D"], wl["lengths"]
+    H, _, n_jobs = shard_of(wl, world, rank)
     T = sum(lengths)
     it = 1.0 / math.sqrt(D)
     g = torch.Generator().manual_seed(1000 + rank)
@@ -273,10 +294,7 @@ def run_ours(args, wl):
     ms = ev0.elapsed_time(ev1)
     check_status()
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
-    tms = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    ms_step = float(tms.item()) / args.steps
+    ms_step = max_over_ranks(ms, world, dev) / args.steps
 
     # ---- per-kernel times (forward / backward-dq / backward-dk,dv), events on the launching stream
     def time_kernel(fn, reps):
@@ -334,13 +352,9 @@ def run_ours(args, wl):
         e2e_step()
     ev1.record()
     sync_all()
-    tms = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    e2e_ms = float(tms.item()) / e2e_steps
+    e2e_ms = max_over_ranks(ev0.elapsed_time(ev1), world, dev) / e2e_steps
 
     if rank == 0:
-        n_jobs = 1 if wl["split_heads"] else world   # weak scaling: every rank ran a whole batch
         flops_job = flops_fwd_bwd(wl["H"], D, lengths) * n_jobs
         tokens_job = T * n_jobs
         value = flops_job / (ms_step * 1e-3) / 1e12
