@@ -150,27 +150,63 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, int ab_format, i
            ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem] ; one thread issues
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+// The issuing thread must stay cheap: a tcgen05.mma of 128 x 128 x 16 occupies the tensor pipe for about 64 cycles, and
+// every instruction the single issuing thread spends between two of them (rebuilding a descriptor costs ~20) shows up
+// as idle tensor time.  So descriptors are built once, kept as two 32-bit halves, and an operand tile further along
+// is addressed by adding a constant (byte offset / 16) to the low half -- the address field cannot carry out of its
+// 14 bits because shared memory ends below 256 KB.
+// The warp that issues the MMAs runs its loops with all 32 lanes (waits, counters and descriptor arithmetic stay
+// warp-uniform and cheap for the scheduler it shares with the row threads); only the tcgen05.mma / tcgen05.commit
+// instructions themselves are predicated on one elected lane (`leader`).  Measured on B200: a single-lane issue loop
+// drops from 65 to 80-100 cycles per MMA when the other warps of the scheduler are busy, the whole-warp form does not.
+struct SmemDesc {
+    uint32_t lo, hi;
+};
+__device__ __forceinline__ SmemDesc make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    SmemDesc d;
+    d.lo = ((saddr & 0x3FFFFu) >> 4) | (((lbo >> 4) & 0x3FFFu) << 16);
+    d.hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);  // version 1, SWIZZLE_128B
+    return d;
+}
+
+// D[tmem] (+)= A[smem] * B[smem] ; one thread issues.  a_off / b_off: byte offsets of the operand tiles.
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ss(bool leader, uint32_t d_tmem, SmemDesc a, uint32_t a_off, SmemDesc b, uint32_t b_off,
+                                       uint32_t idesc) {
+    if (leader) asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a.lo + (a_off >> 4)), "r"(a.hi), "r"(b.lo + (b_off >> 4)), "r"(b.hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
         : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ts(bool leader, uint32_t d_tmem, uint32_t a_tmem, SmemDesc b, uint32_t b_off, uint32_t idesc) {
+    if (leader) asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b.lo + (b_off >> 4)), "r"(b.hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
         : "memory");
 }
+// accumulate chosen at run time (first tile of a work item overwrites)
+__device__ __forceinline__ void mma_ss_dyn(bool leader, uint32_t d_tmem, SmemDesc a, uint32_t a_off, SmemDesc b, uint32_t b_off,
+                                           uint32_t idesc, bool accumulate) {
+    if (accumulate) mma_ss<true>(leader, d_tmem, a, a_off, b, b_off, idesc);
+    else mma_ss<false>(leader, d_tmem, a, a_off, b, b_off, idesc);
+}
+__device__ __forceinline__ void mma_ts_dyn(bool leader, uint32_t d_tmem, uint32_t a_tmem, SmemDesc b, uint32_t b_off, uint32_t idesc,
+                                           bool accumulate) {
+    if (accumulate) mma_ts<true>(leader, d_tmem, a_tmem, b, b_off, idesc);
+    else mma_ts<false>(leader, d_tmem, a_tmem, b, b_off, idesc);
+}
 // the mbarrier receives one arrival when every tcgen05.mma issued so far by this thread has completed
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void mma_commit(bool leader, uint64_t* bar) {
+    if (leader) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

@@ -153,16 +153,19 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
         }
     } else if (warp == 5) {
-        if (lane == 0) {
+        {
+            const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
             constexpr uint32_t idesc_s = make_idesc(kBM, kBK, kF16 ? 0 : 1, 0, 0);
             constexpr uint32_t idesc_dq = make_idesc(kBM, D, kF16 ? 0 : 1, 0, 1);
-            const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+            const SmemDesc desc_q = make_desc(smem_u32(sQ), 0, 1024), desc_do = make_desc(smem_u32(sDO), 0, 1024);
+            const SmemDesc desc_k = make_desc(smem_u32(sK), 0, 1024), desc_v = make_desc(smem_u32(sV), 0, 1024);
+            const SmemDesc desc_kmn = make_desc(smem_u32(sK), kKBox, 1024);  // K tile as MN-major operand of dQ
             uint32_t ph_qf = 0, ph_kf[2] = {0, 0}, ph_vf = 0, ph_ds = 0, ph_free = 1;
             uint32_t kcount = 0;
             bool ok = true;
             SchedConsumer sched;
             int w;
-            while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag)) >= 0) {
+            while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, leader)) >= 0) {
                 const Work wk = fetch_work(a, n_items, w);
                 const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
                 ok = mbar_wait(&bars[A_QDO_FULL], ph_qf, abort_flag);
@@ -170,7 +173,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 if (!ok) break;
                 for (int t = 0; t < n_kh; ++t, ++kcount) {
                     const int st = kcount & 1;
-                    const uint32_t ks = k_addr + st * kKBytes;
+                    const SmemDesc dk = {desc_k.lo + st * (kKBytes >> 4), desc_k.hi};
+                    const SmemDesc dkmn = {desc_kmn.lo + st * (kKBytes >> 4), desc_kmn.hi};
                     ok = mbar_wait(&bars[A_K_FULL0 + st], ph_kf[st], abort_flag);
                     ph_kf[st] ^= 1;
                     if (!ok) break;
@@ -181,18 +185,18 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                     for (int k = 0; k < D / 16; ++k) {
                         const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                        mma_ss(tmem + kColS, make_smem_desc(q_addr + oq, 0, 1024), make_smem_desc(ks + okk, 0, 1024),
-                               idesc_s, k > 0);
+                        if (k == 0) mma_ss<false>(leader, tmem + kColS, desc_q, oq, dk, okk, idesc_s);
+                        else mma_ss<true>(leader, tmem + kColS, desc_q, oq, dk, okk, idesc_s);
                     }
 #pragma unroll
                     for (int k = 0; k < D / 16; ++k) {
                         const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                        mma_ss(tmem + kColDP, make_smem_desc(do_addr + oq, 0, 1024), make_smem_desc(v_addr + okk, 0, 1024),
-                               idesc_s, k > 0);
+                        if (k == 0) mma_ss<false>(leader, tmem + kColDP, desc_do, oq, desc_v, okk, idesc_s);
+                        else mma_ss<true>(leader, tmem + kColDP, desc_do, oq, desc_v, okk, idesc_s);
                     }
-                    mma_commit(&bars[A_SDP_READY]);
-                    mma_commit(&bars[A_V_EMPTY]);
-                    if (t == n_kh - 1) mma_commit(&bars[A_QDO_EMPTY]);
+                    mma_commit(leader, &bars[A_SDP_READY]);
+                    mma_commit(leader, &bars[A_V_EMPTY]);
+                    if (t == n_kh - 1) mma_commit(leader, &bars[A_QDO_EMPTY]);
                     ok = mbar_wait(&bars[A_DS_READY], ph_ds, abort_flag);
                     ph_ds ^= 1;
                     if (!ok) break;
@@ -203,13 +207,14 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     }
                     tc_fence_after();
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k)
-                        mma_ts(tmem + kColDQ, tmem + kColDS + k * 8, make_smem_desc(ks + k * 2048, kKBox, 1024), idesc_dq,
-                               (t > 0 || k > 0) ? 1u : 0u);
-                    mma_commit(&bars[A_K_EMPTY0 + st]);
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        if (k == 0) mma_ts_dyn(leader, tmem + kColDQ, tmem + kColDS, dkmn, 0, idesc_dq, t > 0);
+                        else mma_ts<true>(leader, tmem + kColDQ, tmem + kColDS + k * 8, dkmn, k * 2048, idesc_dq);
+                    }
+                    mma_commit(leader, &bars[A_K_EMPTY0 + st]);
                 }
                 if (!ok) break;
-                mma_commit(&bars[A_DQ_READY]);
+                mma_commit(leader, &bars[A_DQ_READY]);
             }
         }
     } else {
@@ -308,8 +313,17 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 // ================================================================================================ dk/dv kernel
-enum KvBar { B_KV_FULL, B_KV_EMPTY, B_QDO_FULL, B_QDO_EMPTY, B_SDP_READY, B_PDS_TOP, B_PDS_BOT, B_BUF_FREE_A,
-             B_BUF_FREE_B, B_DKV_READY, B_DKV_FREE, B_WORK_FULL0, B_WORK_FULL1, B_WORK_EMPTY0, B_WORK_EMPTY1, kNumKvBars };
+// One block per SM (352 threads): warps 0-3 / 4-7 are two row groups that take the query tiles of a key tile in turn,
+// warp 8 loads K, V (once per item) and the Q tiles (three-stage ring), warp 10 the dO tiles (two-stage ring), warp 9
+// issues every tcgen05.mma.  S and dP live in two rotating buffer pairs in tensor memory, so while one group turns
+// the scores of query tile i+1 into p and ds on the CUDA cores, the tensor cores run dv^T, dk^T of tile i and
+// S, dP of tile i+2.  dO is released as soon as dv^T has consumed it and Q one tile later than needed for S, which
+// hides the TMA latency of the next tiles behind dk^T and S.
+constexpr int kKvThreads = 352;
+constexpr int kQStages = 3, kDoStages = 2, kSdpBufs = 2;
+enum KvBar { B_KV_FULL, B_KV_EMPTY, B_Q_FULL0, B_Q_FULL1, B_Q_FULL2, B_Q_EMPTY0, B_Q_EMPTY1, B_Q_EMPTY2, B_DO_FULL0, B_DO_FULL1,
+             B_DO_EMPTY0, B_DO_EMPTY1, B_SDP_READY0, B_SDP_READY1, B_PDS_READY, B_PDS_FREE, B_DKV_READY, B_DKV_FREE,
+             B_WORK_FULL0, B_WORK_FULL1, B_WORK_EMPTY0, B_WORK_EMPTY1, kNumKvBars };
 
 struct KvWork {
     int h, b, start, len, kh, slot_base, qt0, n_qt;
@@ -359,19 +373,20 @@ __device__ __forceinline__ void kv_chunk(const uint32_t (&s)[32], const uint32_t
 }
 
 template <int D, bool kF16>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kKvThreads, 1)
 tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const KArgs a) {
     constexpr int kBoxes = D / 64;
     constexpr int kQBytes = kBM * D * 2, kKBytes = kBK * D * 2;
-    constexpr int kBufBytes = 64 * 128;  // 64 query rows x 64 keys, 16-bit
-    constexpr uint32_t kColS = 0, kColDP = 64, kColDK = 128, kColDV = 192;
+    constexpr int kBufBytes = 128 * 128;  // 128 query rows x 64 keys, 16-bit
+    constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 320;  // S / dP buffer b at +64*b
+    constexpr uint32_t kCols = 512;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;
     uint8_t* sV = sK + kKBytes;
-    uint8_t* sQ = sV + kKBytes;
-    uint8_t* sDO = sQ + kQBytes;
-    uint8_t* sP = sDO + kQBytes;
+    uint8_t* sQ = sV + kKBytes;                  // kQStages tiles
+    uint8_t* sDO = sQ + kQStages * kQBytes;      // kDoStages tiles
+    uint8_t* sP = sDO + kDoStages * kQBytes;
     uint8_t* sDS = sP + kBufBytes;
     uint64_t* bars = (uint64_t*)(sDS + kBufBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumKvBars);
@@ -380,17 +395,21 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int i = 0; i < kNumKvBars; ++i)
-            mbar_init(&bars[i], (i == B_PDS_TOP || i == B_PDS_BOT) ? 64
-                                : (i == B_DKV_FREE ? 128 : ((i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) ? kRingConsumers : 1)));
-        *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;
+        for (int i = 0; i < kNumKvBars; ++i) {
+            uint32_t cnt = 1;
+            if (i == B_PDS_READY) cnt = 128;
+            if (i == B_DKV_FREE) cnt = 256;
+            if (i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) cnt = 258;  // MMA thread, dO producer, 256 row threads
+            mbar_init(&bars[i], cnt);
+        }
+        *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
         fence_barrier_init();
     }
-    if (warp == 5) {
-        tmem_alloc(tmem_slot, kTmemCols);
+    if (warp == 9) {
+        tmem_alloc(tmem_slot, kCols);
         tmem_relinquish();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == 8 && lane == 0) {
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
@@ -402,18 +421,21 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t tmem = *tmem_slot;
     const int n_items = a.hdr->n_items;
     const int n_work = *abort_flag ? 0 : n_items * a.heads * 2;
+    // G counts query-tile steps over all items of this block: step G uses Q stage G % 3, dO stage G % 2 and
+    // S/dP buffer G % 2; a barrier that completes once per use is in phase (use count) & 1.
 
-    if (warp == 4) {
+    if (warp == 8) {
+        // ------------------------------------------------------------------ TMA: K, V per item, Q ring
         if (lane == 0) {
-            uint32_t ph_kve = 1, ph_qe = 1;
+            uint32_t G = 0, items = 0;
             bool ok = true;
             SchedProducer sched;
             int w;
             while (ok && (w = sched.next(a.sched + 4, n_work, ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
                 const KvWork wk = fetch_kv_work(a, n_items, w);
                 if (!wk.valid) continue;
-                ok = mbar_wait(&bars[B_KV_EMPTY], ph_kve, abort_flag);
-                ph_kve ^= 1;
+                ok = mbar_wait(&bars[B_KV_EMPTY], (items & 1) ^ 1, abort_flag);
+                ++items;
                 if (!ok) break;
                 mbar_expect_tx(&bars[B_KV_FULL], 2 * kKBytes);
 #pragma unroll
@@ -421,100 +443,146 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tma_load_4d(sK + bx * kKBox, &map_k, &bars[B_KV_FULL], bx * 64, wk.start + wk.kh * kBK, wk.h, wk.b);
                     tma_load_4d(sV + bx * kKBox, &map_v, &bars[B_KV_FULL], bx * 64, wk.start + wk.kh * kBK, wk.h, wk.b);
                 }
-                for (int i = wk.qt0; i < wk.n_qt; ++i) {
-                    ok = mbar_wait(&bars[B_QDO_EMPTY], ph_qe, abort_flag);
-                    ph_qe ^= 1;
+                for (int i = wk.qt0; i < wk.n_qt; ++i, ++G) {
+                    const uint32_t st = G % kQStages;
+                    ok = mbar_wait(&bars[B_Q_EMPTY0 + st], ((G / kQStages) & 1) ^ 1, abort_flag);
                     if (!ok) break;
-                    mbar_expect_tx(&bars[B_QDO_FULL], 2 * kQBytes);
+                    mbar_expect_tx(&bars[B_Q_FULL0 + st], kQBytes);
 #pragma unroll
-                    for (int bx = 0; bx < kBoxes; ++bx) {
-                        tma_load_4d(sQ + bx * kQBox, &map_q, &bars[B_QDO_FULL], bx * 64, wk.start + i * kBM, wk.h, wk.b);
-                        tma_load_4d(sDO + bx * kQBox, &map_do, &bars[B_QDO_FULL], bx * 64, wk.start + i * kBM, wk.h, wk.b);
-                    }
+                    for (int bx = 0; bx < kBoxes; ++bx)
+                        tma_load_4d(sQ + st * kQBytes + bx * kQBox, &map_q, &bars[B_Q_FULL0 + st], bx * 64, wk.start + i * kBM, wk.h, wk.b);
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 10) {
+        // ------------------------------------------------------------------ TMA: dO ring
         if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc(kBM, kBK, kF16 ? 0 : 1, 0, 0);
-            constexpr uint32_t idesc_t = make_idesc(D, kBK, kF16 ? 0 : 1, 1, 1);  // (dO^T or Q^T)[D x q] * (P or dS)[q x 64]
-            const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
-            uint32_t ph_kvf = 0, ph_qf = 0, ph_top = 0, ph_bot = 0, ph_free = 1;
+            uint32_t G = 0;
             bool ok = true;
             SchedConsumer sched;
             int w;
             while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
                 const KvWork wk = fetch_kv_work(a, n_items, w);
                 if (!wk.valid) continue;
-                ok = mbar_wait(&bars[B_KV_FULL], ph_kvf, abort_flag);
-                ph_kvf ^= 1;
+                for (int i = wk.qt0; i < wk.n_qt; ++i, ++G) {
+                    const uint32_t st = G % kDoStages;
+                    ok = mbar_wait(&bars[B_DO_EMPTY0 + st], ((G / kDoStages) & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(&bars[B_DO_FULL0 + st], kQBytes);
+#pragma unroll
+                    for (int bx = 0; bx < kBoxes; ++bx)
+                        tma_load_4d(sDO + st * kQBytes + bx * kQBox, &map_do, &bars[B_DO_FULL0 + st], bx * 64, wk.start + i * kBM, wk.h, wk.b);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issuer
+        {
+            const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
+            constexpr uint32_t idesc_s = make_idesc(kBM, kBK, kF16 ? 0 : 1, 0, 0);
+            constexpr uint32_t idesc_t = make_idesc(D, kBK, kF16 ? 0 : 1, 1, 1);  // (dO^T or Q^T)[D x q] * (P or dS)[q x 64]
+            const SmemDesc desc_q = make_desc(smem_u32(sQ), 0, 1024), desc_do = make_desc(smem_u32(sDO), 0, 1024);  // K-major
+            const SmemDesc desc_k = make_desc(smem_u32(sK), 0, 1024), desc_v = make_desc(smem_u32(sV), 0, 1024);
+            const SmemDesc desc_qmn = make_desc(smem_u32(sQ), kQBox, 1024), desc_domn = make_desc(smem_u32(sDO), kQBox, 1024);  // MN-major
+            const SmemDesc desc_p = make_desc(smem_u32(sP), 0, 1024), desc_ds = make_desc(smem_u32(sDS), 0, 1024);
+            uint32_t G = 0, items = 0;
+            bool ok = true;
+            SB_TRACE_DECL(m);
+            // S and dP of step g
+            auto issue_sdp = [&](uint32_t g) {
+                const SmemDesc dq = {desc_q.lo + (g % kQStages) * (kQBytes >> 4), desc_q.hi};
+                const SmemDesc ddo = {desc_do.lo + (g % kDoStages) * (kQBytes >> 4), desc_do.hi};
+                const uint32_t buf = g % kSdpBufs;
+                ok = mbar_wait(&bars[B_Q_FULL0 + g % kQStages], (g / kQStages) & 1, abort_flag);
+                if (!ok) return;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
+                    if (k == 0) mma_ss<false>(leader, tmem + kColS + 64 * buf, dq, oq, desc_k, okk, idesc_s);
+                    else mma_ss<true>(leader, tmem + kColS + 64 * buf, dq, oq, desc_k, okk, idesc_s);
+                }
+                ok = mbar_wait(&bars[B_DO_FULL0 + g % kDoStages], (g / kDoStages) & 1, abort_flag);
+                if (!ok) return;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
+                    if (k == 0) mma_ss<false>(leader, tmem + kColDP + 64 * buf, ddo, oq, desc_v, okk, idesc_s);
+                    else mma_ss<true>(leader, tmem + kColDP + 64 * buf, ddo, oq, desc_v, okk, idesc_s);
+                }
+                mma_commit(leader, &bars[B_SDP_READY0 + buf]);
+            };
+            SchedConsumer sched;
+            int w;
+            while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, leader)) >= 0) {
+                const KvWork wk = fetch_kv_work(a, n_items, w);
+                if (!wk.valid) continue;
+                const int n = wk.n_qt - wk.qt0;
+                ok = mbar_wait(&bars[B_KV_FULL], items & 1, abort_flag);
                 if (!ok) break;
-                for (int i = wk.qt0; i < wk.n_qt; ++i) {
-                    ok = mbar_wait(&bars[B_QDO_FULL], ph_qf, abort_flag);
-                    ph_qf ^= 1;
+                issue_sdp(G);
+                if (ok && n > 1) issue_sdp(G + 1);
+                if (ok && n <= 2) mma_commit(leader, &bars[B_KV_EMPTY]);
+                for (int j = 0; ok && j < n; ++j) {
+                    const uint32_t g = G + j;
+                    SB_TRACE_EV(m, 0, 1);
+                    ok = mbar_wait(&bars[B_PDS_READY], g & 1, abort_flag);
                     if (!ok) break;
+                    SB_TRACE_EV(m, 0, 2);
+                    if (j == 0) {  // the previous item's accumulators must have been read out
+                        ok = mbar_wait(&bars[B_DKV_FREE], (items & 1) ^ 1, abort_flag);
+                        if (!ok) break;
+                    }
                     tc_fence_after();
+                    const SmemDesc dqmn = {desc_qmn.lo + (g % kQStages) * (kQBytes >> 4), desc_qmn.hi};
+                    const SmemDesc ddomn = {desc_domn.lo + (g % kDoStages) * (kQBytes >> 4), desc_domn.hi};
 #pragma unroll
-                    for (int k = 0; k < D / 16; ++k) {
-                        const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                        mma_ss(tmem + kColS, make_smem_desc(q_addr + oq, 0, 1024), make_smem_desc(k_addr + okk, 0, 1024),
-                               idesc_s, k > 0);
+                    for (int kk = 0; kk < 8; ++kk) {
+                        if (kk == 0) mma_ss_dyn(leader, tmem + kColDV, ddomn, 0, desc_p, 0, idesc_t, j > 0);
+                        else mma_ss<true>(leader, tmem + kColDV, ddomn, kk * 2048, desc_p, kk * 2048, idesc_t);
                     }
+                    mma_commit(leader, &bars[B_DO_EMPTY0 + g % kDoStages]);
 #pragma unroll
-                    for (int k = 0; k < D / 16; ++k) {
-                        const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                        mma_ss(tmem + kColDP, make_smem_desc(do_addr + oq, 0, 1024), make_smem_desc(v_addr + okk, 0, 1024),
-                               idesc_s, k > 0);
+                    for (int kk = 0; kk < 8; ++kk) {
+                        if (kk == 0) mma_ss_dyn(leader, tmem + kColDK, dqmn, 0, desc_ds, 0, idesc_t, j > 0);
+                        else mma_ss<true>(leader, tmem + kColDK, dqmn, kk * 2048, desc_ds, kk * 2048, idesc_t);
                     }
-                    mma_commit(&bars[B_SDP_READY]);
-                    if (i == wk.n_qt - 1) mma_commit(&bars[B_KV_EMPTY]);
-                    if (i == wk.qt0) {  // the previous item's accumulators must have been read out
-                        ok = mbar_wait(&bars[B_DKV_FREE], ph_free, abort_flag);
-                        ph_free ^= 1;
-                        if (!ok) break;
+                    mma_commit(leader, &bars[B_Q_EMPTY0 + g % kQStages]);
+                    mma_commit(leader, &bars[B_PDS_FREE]);
+                    SB_TRACE_EV(m, 0, 3);
+                    if (j + 2 < n) {
+                        issue_sdp(g + 2);
+                        if (ok && j + 3 == n) mma_commit(leader, &bars[B_KV_EMPTY]);
                     }
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        ok = mbar_wait(&bars[half == 0 ? B_PDS_TOP : B_PDS_BOT], half == 0 ? ph_top : ph_bot, abort_flag);
-                        if (half == 0) ph_top ^= 1; else ph_bot ^= 1;
-                        if (!ok) break;
-                        tc_fence_after();
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            const uint32_t acc = (i > wk.qt0 || half > 0 || kk > 0) ? 1u : 0u;
-                            const uint32_t oa = (half * 4 + kk) * 2048, ob = kk * 2048;
-                            mma_ss(tmem + kColDV, make_smem_desc(do_addr + oa, kQBox, 1024), make_smem_desc(p_addr + ob, 0, 1024),
-                                   idesc_t, acc);
-                            mma_ss(tmem + kColDK, make_smem_desc(q_addr + oa, kQBox, 1024), make_smem_desc(ds_addr + ob, 0, 1024),
-                                   idesc_t, acc);
-                        }
-                        mma_commit(&bars[half == 0 ? B_BUF_FREE_A : B_BUF_FREE_B]);
-                    }
-                    if (!ok) break;
-                    mma_commit(&bars[B_QDO_EMPTY]);
+                    SB_TRACE_EV(m, 0, 4);
                 }
                 if (!ok) break;
-                mma_commit(&bars[B_DKV_READY]);
+                mma_commit(leader, &bars[B_DKV_READY]);
+                G += n;
+                ++items;
             }
         }
     } else {
-        const int r = tid;
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        // ------------------------------------------------------------------ row groups
+        const int grp = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const float scale = a.inv_temp * kLog2e;
-        const bool top = warp < 2;
-        uint8_t* prow = sP + (r & 63) * 128;
-        uint8_t* srow = sDS + (r & 63) * 128;
-        uint32_t ph_sdp = 0, ph_buf = top ? 1 : 0, ph_dkv = 0;
+        uint8_t* prow = sP + r * 128;
+        uint8_t* srow = sDS + r * 128;
+        uint32_t G = 0, items = 0;
         bool ok = true;
+        SB_TRACE_DECL(c);
         SchedConsumer sched;
         int w;
         while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
             const KvWork wk = fetch_kv_work(a, n_items, w);
             if (!wk.valid) continue;
+            const int n = wk.n_qt - wk.qt0;
             const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             const float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
-            // per-row scalars of a step (carry of W, prefix of g, drem): loaded one step ahead
+            // per-row scalars of a step (carry of W, prefix of g, drem): loaded one step of this group ahead
             float nW = 0.f, nC = 0.f, nD = 0.f;
             auto load_scalars = [&](int i) {
                 const int qi = i * kBM + r;
@@ -528,15 +596,18 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     nD = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
                 }
             };
-            load_scalars(wk.qt0);
-            for (int i = wk.qt0; i < wk.n_qt; ++i) {
+            load_scalars(wk.qt0 + grp);
+            for (int j = grp; j < n; j += 2) {
+                const int i = wk.qt0 + j;
+                const uint32_t g = G + j, buf = g % kSdpBufs;
                 const int qi = i * kBM + r;
                 float W = nW;
                 const float cright = nC, drem = nD;
-                load_scalars(i + 1);
-                ok = mbar_wait(&bars[B_SDP_READY], ph_sdp, abort_flag);
-                ph_sdp ^= 1;
+                load_scalars(i + 2);
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 1);
+                ok = mbar_wait(&bars[B_SDP_READY0 + buf], (g / kSdpBufs) & 1, abort_flag);
                 if (!ok) break;
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 2);
                 tc_fence_after();
                 const bool masked = i == wk.qt0;
                 const int lim = min(kBK, max(0, qi - wk.kh * kBK + a.attend_current));
@@ -544,22 +615,25 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 float sfx = 0.f;
                 {
                     uint32_t s[32], dp[32];
-                    tmem_ld32(lane_base + kColS + 32, s);
-                    tmem_ld32(lane_base + kColDP + 32, dp);
+                    tmem_ld32(lane_base + kColS + 64 * buf + 32, s);
+                    tmem_ld32(lane_base + kColDP + 64 * buf + 32, dp);
                     tmem_wait_ld();
                     if (masked) kv_chunk<true, kF16>(s, dp, scale, 32, lim, drem, cright, W, sfx, pp + 16, ps + 16);
                     else kv_chunk<false, kF16>(s, dp, scale, 32, lim, drem, cright, W, sfx, pp + 16, ps + 16);
-                    tmem_ld32(lane_base + kColS, s);
-                    tmem_ld32(lane_base + kColDP, dp);
+                    tmem_ld32(lane_base + kColS + 64 * buf, s);
+                    tmem_ld32(lane_base + kColDP + 64 * buf, dp);
                     tmem_wait_ld();
                     if (masked) kv_chunk<true, kF16>(s, dp, scale, 0, lim, drem, cright, W, sfx, pp, ps);
                     else kv_chunk<false, kF16>(s, dp, scale, 0, lim, drem, cright, W, sfx, pp, ps);
                 }
                 tc_fence_before();
-                // rows 0-63 write first; rows 64-127 reuse the buffers once the first half has been consumed
-                ok = mbar_wait(&bars[top ? B_BUF_FREE_B : B_BUF_FREE_A], ph_buf, abort_flag);
-                ph_buf ^= 1;
-                if (!ok) break;
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 3);
+                // the p / ds tiles of the previous step must have been consumed by its dv^T, dk^T
+                if (g > 0) {
+                    ok = mbar_wait(&bars[B_PDS_FREE], (g - 1) & 1, abort_flag);
+                    if (!ok) break;
+                }
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 4);
 #pragma unroll
                 for (int ch = 0; ch < 8; ++ch) {
                     const int off = (ch ^ (r & 7)) << 4;
@@ -567,34 +641,33 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     *(uint4*)(srow + off) = make_uint4(ps[4 * ch], ps[4 * ch + 1], ps[4 * ch + 2], ps[4 * ch + 3]);
                 }
                 fence_async_smem();
-                mbar_arrive(&bars[top ? B_PDS_TOP : B_PDS_BOT]);
+                mbar_arrive(&bars[B_PDS_READY]);
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 5);
             }
             if (!ok) break;
-            // epilogue: this thread holds one head-dim index d of dk^T and dv^T, the 64 keys along the columns
-            ok = mbar_wait(&bars[B_DKV_READY], ph_dkv, abort_flag);
-            ph_dkv ^= 1;
+            // epilogue: group 0 stores dk, group 1 dv; a thread holds one head-dim index d, the 64 keys along the columns
+            ok = mbar_wait(&bars[B_DKV_READY], items & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const int d = D == 128 ? r : (warp * 16 + lane);
+            const int d = D == 128 ? r : ((warp & 3) * 16 + lane);
             const bool d_ok = D == 128 ? true : lane < 16;
             const int keys_valid = min(kBK, wk.len - wk.kh * kBK);
-#pragma unroll
-            for (int which = 0; which < 2; ++which) {
-                const MatView& m = which == 0 ? a.dk : a.dv;
-                const float sc = which == 0 ? a.inv_temp : 1.f;
+            {
+                const MatView& m = grp == 0 ? a.dk : a.dv;
+                const float sc = grp == 0 ? a.inv_temp : 1.f;
                 char* base = m.ptr + 2 * ((int64_t)wk.b * m.sb + (int64_t)wk.h * m.sh +
                                           (int64_t)(wk.start + wk.kh * kBK) * m.st + d);
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     uint32_t v[32];
-                    tmem_ld32(lane_base + (which == 0 ? kColDK : kColDV) + half * 32, v);
+                    tmem_ld32(lane_base + (grp == 0 ? kColDK : kColDV) + half * 32, v);
                     tmem_wait_ld();
                     if (d_ok) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int key = half * 32 + j;
+                        for (int jj = 0; jj < 32; ++jj) {
+                            const int key = half * 32 + jj;
                             if (key < keys_valid) {
-                                const float x = __uint_as_float(v[j]) * sc;
+                                const float x = __uint_as_float(v[jj]) * sc;
                                 char* ptr = base + 2 * (int64_t)key * m.st;
                                 if (kF16) *(__half*)ptr = __float2half_rn(x);
                                 else *(__nv_bfloat16*)ptr = __float2bfloat16_rn(x);
@@ -605,9 +678,11 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             tc_fence_before();
             mbar_arrive(&bars[B_DKV_FREE]);
+            G += n;
+            ++items;
         }
     }
-    tc_teardown(abort_flag, a.status, tmem, kTmemCols, 5);
+    tc_teardown(abort_flag, a.status, tmem, kCols, 9);
     sched_finish(a.sched + 4);
 }
 
@@ -623,10 +698,10 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         return 1;
     // both kernels: 2 x (128 x D) + 3 x (64 x D) 16-bit tiles (dq: q, do, 2 k stages, v; dk/dv: k, v, q, do, p, ds)
     constexpr int need = 2 * kBM * D * 2 + 3 * kBK * D * 2 + 256;
-    constexpr int need_b = 2 * kBM * D * 2 + 2 * kBK * D * 2 + 2 * 64 * 128 + 256;
+    constexpr int need_b = (kQStages + kDoStages) * kBM * D * 2 + 2 * kBK * D * 2 + 2 * 128 * 128 + 512;
     // at least 80 KB so that never more than two blocks (2 x 256 tensor-memory columns) share an SM
     constexpr int smem_a = need > 81920 ? need : 81920;
-    constexpr int smem_b = need_b > 81920 ? need_b : 81920;
+    constexpr int smem_b = need_b > 120 * 1024 ? need_b : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
     cudaError_t e = cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_b);
@@ -637,7 +712,7 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     if (p.bwd_phases != SBATTN_BWD_DKDV) tc_bwd_dq_kernel<D, kF16><<<grid, kThreads, smem_a, st>>>(mq, mk, mv, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<grid, kThreads, smem_b, st>>>(mq, mk, mv, mdo, a);
+    if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk, mv, mdo, a);
     return (int)cudaGetLastError();
 }
 

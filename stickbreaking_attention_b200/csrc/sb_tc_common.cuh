@@ -89,13 +89,15 @@ struct SchedProducer {
 struct SchedConsumer {
     int i = 0;
     uint32_t ph[kRing] = {0, 0};
-    __device__ __forceinline__ int next(SchedRing* ring, uint64_t* full, uint64_t* empty, volatile uint32_t* abort_flag) {
+    // `arrive`: false for all but one lane when a whole warp consumes together (the slot counts one arrival per consumer)
+    __device__ __forceinline__ int next(SchedRing* ring, uint64_t* full, uint64_t* empty, volatile uint32_t* abort_flag,
+                                        bool arrive = true) {
         const int sl = i & (kRing - 1);
         ++i;
         if (!sm100::mbar_wait(&full[sl], ph[sl], abort_flag)) return -1;
         ph[sl] ^= 1;
         const int w = ((volatile SchedRing*)ring)->slot[sl];
-        sm100::mbar_arrive(&empty[sl]);
+        if (arrive) sm100::mbar_arrive(&empty[sl]);
         return w;
     }
 };

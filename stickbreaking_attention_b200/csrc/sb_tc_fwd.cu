@@ -181,10 +181,13 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        {
+            const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
             constexpr uint32_t idesc_s = make_idesc(kBM, kBN, kF16 ? 0 : 1, 0, 0);
             constexpr uint32_t idesc_o = make_idesc(kBM, D, kF16 ? 0 : 1, 0, 1);
-            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+            const SmemDesc desc_q = make_desc(smem_u32(sQ), 0, 1024);          // K-major operands of S
+            const SmemDesc desc_k = make_desc(smem_u32(sK), 0, 1024);
+            const SmemDesc desc_v = make_desc(smem_u32(sV), kBoxBytes, 1024);  // MN-major operand of P V
             uint32_t ph_qf = 0, ph_kf = 0, ph_vf0 = 0, ph_vf1 = 0, ph_of = 1;  // bit i of ph_kf: K stage i
             uint32_t ph_p = 0;   // bit i: parity of P_READY of S buffer i
             uint32_t sbuf = 0;   // running step count modulo 3 = S buffer of the next S to issue
@@ -200,21 +203,22 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 ph_kf ^= 1u << st;
                 if (!ok) return;
                 tc_fence_after();
-                const uint32_t kk = k_addr + st * kTileBytes;
+                const SmemDesc dk = {desc_k.lo + st * (kTileBytes >> 4), desc_k.hi};
+                const uint32_t d_s = tmem + kColS0 + 128 * sbuf;
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
                     const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-                    mma_ss(tmem + kColS0 + 128 * sbuf, make_smem_desc(q_addr + off, 0, 1024),
-                           make_smem_desc(kk + off, 0, 1024), idesc_s, k > 0);
+                    if (k == 0) mma_ss<false>(leader, d_s, desc_q, off, dk, off, idesc_s);
+                    else mma_ss<true>(leader, d_s, desc_q, off, dk, off, idesc_s);
                 }
-                mma_commit(&bars[S_READY0 + sbuf]);
+                mma_commit(leader, &bars[S_READY0 + sbuf]);
                 sbuf = sbuf == 2 ? 0 : sbuf + 1;
-                mma_commit(&bars[K_EMPTY0 + st]);
-                if (j == n - 1) mma_commit(&bars[Q_EMPTY]);
+                mma_commit(leader, &bars[K_EMPTY0 + st]);
+                if (j == n - 1) mma_commit(leader, &bars[Q_EMPTY]);
             };
             SchedConsumer sched;
             int w;
-            while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
+            while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag, leader)) >= 0) {
                 const Work wk = fetch_work(a, n_items, w);
                 const int n = wk.qt + 1;
                 ok = mbar_wait(&bars[Q_FULL], ph_qf, abort_flag);
@@ -243,18 +247,20 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         if (!ok) break;
                     }
                     tc_fence_after();
-                    const uint32_t vv = v_addr + st * kTileBytes;
+                    const SmemDesc dv = {desc_v.lo + st * (kTileBytes >> 4), desc_v.hi};
+                    const uint32_t a_p = tmem + kColS0 + 128 * b + kColPOff;
 #pragma unroll
-                    for (int k = 0; k < kBN / 16; ++k)
-                        mma_ts(tmem + kColO, tmem + kColS0 + 128 * b + kColPOff + k * 8,
-                               make_smem_desc(vv + k * 2048, kBoxBytes, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-                    mma_commit(&bars[V_EMPTY0 + st]);
+                    for (int k = 0; k < kBN / 16; ++k) {
+                        if (k == 0) mma_ts_dyn(leader, tmem + kColO, a_p, dv, 0, idesc_o, j > 0);
+                        else mma_ts<true>(leader, tmem + kColO, a_p + k * 8, dv, k * 2048, idesc_o);
+                    }
+                    mma_commit(leader, &bars[V_EMPTY0 + st]);
                     SB_TRACE_EV(m, 0, 3);
                     if (j + 3 < n) issue_s(j + 3, n);
                     SB_TRACE_EV(m, 0, 4);
                 }
                 if (!ok) break;
-                mma_commit(&bars[O_READY]);
+                mma_commit(leader, &bars[O_READY]);
             }
         }
     } else {
