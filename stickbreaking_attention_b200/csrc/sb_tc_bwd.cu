@@ -313,40 +313,35 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 // ================================================================================================ dk/dv kernel
-// One block per SM (352 threads): warps 0-3 / 4-7 are two row groups that take the query tiles of a key tile in turn,
-// warp 8 loads K, V (once per item) and the Q tiles (three-stage ring), warp 10 the dO tiles (two-stage ring), warp 9
-// issues every tcgen05.mma.  S and dP live in two rotating buffer pairs in tensor memory, so while one group turns
-// the scores of query tile i+1 into p and ds on the CUDA cores, the tensor cores run dv^T, dk^T of tile i and
-// S, dP of tile i+2.  dO is released as soon as dv^T has consumed it and Q one tile later than needed for S, which
-// hides the TMA latency of the next tiles behind dk^T and S.
+// One block per SM (352 threads) keeps a 128-key tile stationary: warps 0-3 own its right 64 keys, warps 4-7 its left
+// 64 keys (one thread per query row in each group; the halves are independent because carry_w / carry_c exist at every
+// 64-key boundary), warp 8 loads K, V (once per item) and the Q tiles (two-stage ring), warp 10 the dO tiles, warp 9
+// issues every tcgen05.mma.  All four contractions run with N = 128, the widest shape the tensor-memory budget allows:
+// S and dP [128 q x 128 keys], dv^T and dk^T [D x 128 keys] (an MMA instruction costs the same ~65 cycles for N = 64 and
+// N = 128, so narrow tiles waste half of the tensor pipe).  dO is released as soon as dv^T has consumed it and Q one
+// tile later than needed for S, which hides most of the TMA latency of the next tile behind dk^T and S.
 constexpr int kKvThreads = 352;
-constexpr int kQStages = 3, kDoStages = 2, kSdpBufs = 2;
-enum KvBar { B_KV_FULL, B_KV_EMPTY, B_Q_FULL0, B_Q_FULL1, B_Q_FULL2, B_Q_EMPTY0, B_Q_EMPTY1, B_Q_EMPTY2, B_DO_FULL0, B_DO_FULL1,
-             B_DO_EMPTY0, B_DO_EMPTY1, B_SDP_READY0, B_SDP_READY1, B_PDS_READY, B_PDS_FREE, B_DKV_READY, B_DKV_FREE,
-             B_WORK_FULL0, B_WORK_FULL1, B_WORK_EMPTY0, B_WORK_EMPTY1, kNumKvBars };
+constexpr int kKT = 128;  // keys per stationary tile
+enum KvBar { B_KV_FULL, B_KV_EMPTY, B_Q_FULL0, B_Q_FULL1, B_Q_EMPTY0, B_Q_EMPTY1, B_DO_FULL, B_DO_EMPTY, B_SDP_READY, B_PDS_READY,
+             B_DKV_READY, B_DKV_FREE, B_WORK_FULL0, B_WORK_FULL1, B_WORK_EMPTY0, B_WORK_EMPTY1, kNumKvBars };
 
 struct KvWork {
-    int h, b, start, len, kh, slot_base, qt0, n_qt;
-    bool valid;
+    int h, b, start, len, kt, slot_base, n_qt;
 };
 __device__ __forceinline__ KvWork fetch_kv_work(const KArgs& a, int n_items, int w) {
-    // groups of head_group heads; inside a group the 64-key tiles heaviest first (key tiles are heaviest where
-    // query tiles are lightest: the item table is walked backwards), the two halves of a 128-row item and the heads
-    // of the group innermost
-    const int per_group = n_items * 2 * a.head_group;
+    // groups of head_group heads; inside a group the 128-key tiles heaviest first (key tiles are heaviest where
+    // query tiles are lightest: the item table is walked backwards), the heads of the group innermost
+    const int per_group = n_items * a.head_group;
     const int g = w / per_group, rest = w - g * per_group;
     const int hg = min(a.head_group, a.heads - g * a.head_group);
-    const int idx = rest / (2 * hg), rem = rest - idx * 2 * hg;
-    const int half = rem / hg;
+    const int idx = rest / hg;
     const int2 it = a.items[n_items - 1 - idx];
     const SeqInfo s = a.seqs[it.x];
     KvWork k;
-    k.h = g * a.head_group + rem - half * hg;
+    k.h = g * a.head_group + rest - idx * hg;
     k.b = s.batch; k.start = s.start; k.len = s.len; k.slot_base = s.slot_base;
-    k.kh = 2 * it.y + half;
-    k.qt0 = it.y;
+    k.kt = it.y;
     k.n_qt = (s.len + kBM - 1) / kBM;
-    k.valid = k.kh * kBK < s.len;
     return k;
 }
 
@@ -377,16 +372,16 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const KArgs a) {
     constexpr int kBoxes = D / 64;
-    constexpr int kQBytes = kBM * D * 2, kKBytes = kBK * D * 2;
-    constexpr int kBufBytes = 128 * 128;  // 128 query rows x 64 keys, 16-bit
-    constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 320;  // S / dP buffer b at +64*b
+    constexpr int kQBytes = kBM * D * 2;     // a 128-row tile of Q, dO, K or V
+    constexpr int kBufBytes = 2 * 128 * 128;  // 128 query rows x 128 keys, 16-bit, as two 64-key blocks
+    constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 384;
     constexpr uint32_t kCols = 512;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;
-    uint8_t* sV = sK + kKBytes;
-    uint8_t* sQ = sV + kKBytes;                  // kQStages tiles
-    uint8_t* sDO = sQ + kQStages * kQBytes;      // kDoStages tiles
-    uint8_t* sP = sDO + kDoStages * kQBytes;
+    uint8_t* sV = sK + kQBytes;
+    uint8_t* sQ = sV + kQBytes;          // two stages
+    uint8_t* sDO = sQ + 2 * kQBytes;
+    uint8_t* sP = sDO + kQBytes;
     uint8_t* sDS = sP + kBufBytes;
     uint64_t* bars = (uint64_t*)(sDS + kBufBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumKvBars);
@@ -397,9 +392,8 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (tid == 0) {
         for (int i = 0; i < kNumKvBars; ++i) {
             uint32_t cnt = 1;
-            if (i == B_PDS_READY) cnt = 128;
-            if (i == B_DKV_FREE) cnt = 256;
-            if (i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) cnt = 258;  // MMA thread, dO producer, 256 row threads
+            if (i == B_PDS_READY || i == B_DKV_FREE) cnt = 256;
+            if (i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) cnt = 258;  // MMA warp (one lane), dO producer, 256 row threads
             mbar_init(&bars[i], cnt);
         }
         *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
@@ -420,9 +414,9 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const int n_items = a.hdr->n_items;
-    const int n_work = *abort_flag ? 0 : n_items * a.heads * 2;
-    // G counts query-tile steps over all items of this block: step G uses Q stage G % 3, dO stage G % 2 and
-    // S/dP buffer G % 2; a barrier that completes once per use is in phase (use count) & 1.
+    const int n_work = *abort_flag ? 0 : n_items * a.heads;
+    // G counts query-tile steps over all items of this block: step G uses Q stage G & 1; a barrier that completes
+    // once per use is in phase (use count) & 1.
 
     if (warp == 8) {
         // ------------------------------------------------------------------ TMA: K, V per item, Q ring
@@ -433,19 +427,18 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             int w;
             while (ok && (w = sched.next(a.sched + 4, n_work, ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
                 const KvWork wk = fetch_kv_work(a, n_items, w);
-                if (!wk.valid) continue;
                 ok = mbar_wait(&bars[B_KV_EMPTY], (items & 1) ^ 1, abort_flag);
                 ++items;
                 if (!ok) break;
-                mbar_expect_tx(&bars[B_KV_FULL], 2 * kKBytes);
+                mbar_expect_tx(&bars[B_KV_FULL], 2 * kQBytes);
 #pragma unroll
                 for (int bx = 0; bx < kBoxes; ++bx) {
-                    tma_load_4d(sK + bx * kKBox, &map_k, &bars[B_KV_FULL], bx * 64, wk.start + wk.kh * kBK, wk.h, wk.b);
-                    tma_load_4d(sV + bx * kKBox, &map_v, &bars[B_KV_FULL], bx * 64, wk.start + wk.kh * kBK, wk.h, wk.b);
+                    tma_load_4d(sK + bx * kQBox, &map_k, &bars[B_KV_FULL], bx * 64, wk.start + wk.kt * kKT, wk.h, wk.b);
+                    tma_load_4d(sV + bx * kQBox, &map_v, &bars[B_KV_FULL], bx * 64, wk.start + wk.kt * kKT, wk.h, wk.b);
                 }
-                for (int i = wk.qt0; i < wk.n_qt; ++i, ++G) {
-                    const uint32_t st = G % kQStages;
-                    ok = mbar_wait(&bars[B_Q_EMPTY0 + st], ((G / kQStages) & 1) ^ 1, abort_flag);
+                for (int i = wk.kt; i < wk.n_qt; ++i, ++G) {
+                    const uint32_t st = G & 1;
+                    ok = mbar_wait(&bars[B_Q_EMPTY0 + st], ((G >> 1) & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(&bars[B_Q_FULL0 + st], kQBytes);
 #pragma unroll
@@ -455,7 +448,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
         }
     } else if (warp == 10) {
-        // ------------------------------------------------------------------ TMA: dO ring
+        // ------------------------------------------------------------------ TMA: dO (single stage)
         if (lane == 0) {
             uint32_t G = 0;
             bool ok = true;
@@ -463,15 +456,13 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             int w;
             while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
                 const KvWork wk = fetch_kv_work(a, n_items, w);
-                if (!wk.valid) continue;
-                for (int i = wk.qt0; i < wk.n_qt; ++i, ++G) {
-                    const uint32_t st = G % kDoStages;
-                    ok = mbar_wait(&bars[B_DO_EMPTY0 + st], ((G / kDoStages) & 1) ^ 1, abort_flag);
+                for (int i = wk.kt; i < wk.n_qt; ++i, ++G) {
+                    ok = mbar_wait(&bars[B_DO_EMPTY], (G & 1) ^ 1, abort_flag);
                     if (!ok) break;
-                    mbar_expect_tx(&bars[B_DO_FULL0 + st], kQBytes);
+                    mbar_expect_tx(&bars[B_DO_FULL], kQBytes);
 #pragma unroll
                     for (int bx = 0; bx < kBoxes; ++bx)
-                        tma_load_4d(sDO + st * kQBytes + bx * kQBox, &map_do, &bars[B_DO_FULL0 + st], bx * 64, wk.start + i * kBM, wk.h, wk.b);
+                        tma_load_4d(sDO + bx * kQBox, &map_do, &bars[B_DO_FULL], bx * 64, wk.start + i * kBM, wk.h, wk.b);
                 }
             }
         }
@@ -479,82 +470,67 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // ------------------------------------------------------------------ MMA issuer
         {
             const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
-            constexpr uint32_t idesc_s = make_idesc(kBM, kBK, kF16 ? 0 : 1, 0, 0);
-            constexpr uint32_t idesc_t = make_idesc(D, kBK, kF16 ? 0 : 1, 1, 1);  // (dO^T or Q^T)[D x q] * (P or dS)[q x 64]
+            constexpr uint32_t idesc_s = make_idesc(kBM, kKT, kF16 ? 0 : 1, 0, 0);
+            constexpr uint32_t idesc_t = make_idesc(D, kKT, kF16 ? 0 : 1, 1, 1);  // (dO^T or Q^T)[D x q] * (P or dS)[q x 128]
             const SmemDesc desc_q = make_desc(smem_u32(sQ), 0, 1024), desc_do = make_desc(smem_u32(sDO), 0, 1024);  // K-major
             const SmemDesc desc_k = make_desc(smem_u32(sK), 0, 1024), desc_v = make_desc(smem_u32(sV), 0, 1024);
             const SmemDesc desc_qmn = make_desc(smem_u32(sQ), kQBox, 1024), desc_domn = make_desc(smem_u32(sDO), kQBox, 1024);  // MN-major
-            const SmemDesc desc_p = make_desc(smem_u32(sP), 0, 1024), desc_ds = make_desc(smem_u32(sDS), 0, 1024);
+            const SmemDesc desc_p = make_desc(smem_u32(sP), kQBox, 1024), desc_ds = make_desc(smem_u32(sDS), kQBox, 1024);
             uint32_t G = 0, items = 0;
             bool ok = true;
             SB_TRACE_DECL(m);
-            // S and dP of step g
-            auto issue_sdp = [&](uint32_t g) {
-                const SmemDesc dq = {desc_q.lo + (g % kQStages) * (kQBytes >> 4), desc_q.hi};
-                const SmemDesc ddo = {desc_do.lo + (g % kDoStages) * (kQBytes >> 4), desc_do.hi};
-                const uint32_t buf = g % kSdpBufs;
-                ok = mbar_wait(&bars[B_Q_FULL0 + g % kQStages], (g / kQStages) & 1, abort_flag);
-                if (!ok) return;
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < D / 16; ++k) {
-                    const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                    if (k == 0) mma_ss<false>(leader, tmem + kColS + 64 * buf, dq, oq, desc_k, okk, idesc_s);
-                    else mma_ss<true>(leader, tmem + kColS + 64 * buf, dq, oq, desc_k, okk, idesc_s);
-                }
-                ok = mbar_wait(&bars[B_DO_FULL0 + g % kDoStages], (g / kDoStages) & 1, abort_flag);
-                if (!ok) return;
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < D / 16; ++k) {
-                    const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                    if (k == 0) mma_ss<false>(leader, tmem + kColDP + 64 * buf, ddo, oq, desc_v, okk, idesc_s);
-                    else mma_ss<true>(leader, tmem + kColDP + 64 * buf, ddo, oq, desc_v, okk, idesc_s);
-                }
-                mma_commit(leader, &bars[B_SDP_READY0 + buf]);
-            };
             SchedConsumer sched;
             int w;
             while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, leader)) >= 0) {
                 const KvWork wk = fetch_kv_work(a, n_items, w);
-                if (!wk.valid) continue;
-                const int n = wk.n_qt - wk.qt0;
+                const int n = wk.n_qt - wk.kt;
                 ok = mbar_wait(&bars[B_KV_FULL], items & 1, abort_flag);
-                if (!ok) break;
-                issue_sdp(G);
-                if (ok && n > 1) issue_sdp(G + 1);
-                if (ok && n <= 2) mma_commit(leader, &bars[B_KV_EMPTY]);
                 for (int j = 0; ok && j < n; ++j) {
-                    const uint32_t g = G + j;
+                    const uint32_t g = G + j, st = g & 1;
+                    const SmemDesc dq = {desc_q.lo + st * (kQBytes >> 4), desc_q.hi};
+                    const SmemDesc dqmn = {desc_qmn.lo + st * (kQBytes >> 4), desc_qmn.hi};
                     SB_TRACE_EV(m, 0, 1);
+                    ok = mbar_wait(&bars[B_Q_FULL0 + st], (g >> 1) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint32_t o = (k >> 2) * kQBox + (k & 3) * 32;
+                        if (k == 0) mma_ss<false>(leader, tmem + kColS, dq, o, desc_k, o, idesc_s);
+                        else mma_ss<true>(leader, tmem + kColS, dq, o, desc_k, o, idesc_s);
+                    }
+                    ok = mbar_wait(&bars[B_DO_FULL], g & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint32_t o = (k >> 2) * kQBox + (k & 3) * 32;
+                        if (k == 0) mma_ss<false>(leader, tmem + kColDP, desc_do, o, desc_v, o, idesc_s);
+                        else mma_ss<true>(leader, tmem + kColDP, desc_do, o, desc_v, o, idesc_s);
+                    }
+                    mma_commit(leader, &bars[B_SDP_READY]);
+                    if (j == n - 1) mma_commit(leader, &bars[B_KV_EMPTY]);
+                    SB_TRACE_EV(m, 0, 2);
                     ok = mbar_wait(&bars[B_PDS_READY], g & 1, abort_flag);
                     if (!ok) break;
-                    SB_TRACE_EV(m, 0, 2);
+                    SB_TRACE_EV(m, 0, 3);
                     if (j == 0) {  // the previous item's accumulators must have been read out
                         ok = mbar_wait(&bars[B_DKV_FREE], (items & 1) ^ 1, abort_flag);
                         if (!ok) break;
                     }
                     tc_fence_after();
-                    const SmemDesc dqmn = {desc_qmn.lo + (g % kQStages) * (kQBytes >> 4), desc_qmn.hi};
-                    const SmemDesc ddomn = {desc_domn.lo + (g % kDoStages) * (kQBytes >> 4), desc_domn.hi};
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {
-                        if (kk == 0) mma_ss_dyn(leader, tmem + kColDV, ddomn, 0, desc_p, 0, idesc_t, j > 0);
-                        else mma_ss<true>(leader, tmem + kColDV, ddomn, kk * 2048, desc_p, kk * 2048, idesc_t);
+                        if (kk == 0) mma_ss_dyn(leader, tmem + kColDV, desc_domn, 0, desc_p, 0, idesc_t, j > 0);
+                        else mma_ss<true>(leader, tmem + kColDV, desc_domn, kk * 2048, desc_p, kk * 2048, idesc_t);
                     }
-                    mma_commit(leader, &bars[B_DO_EMPTY0 + g % kDoStages]);
+                    mma_commit(leader, &bars[B_DO_EMPTY]);
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {
                         if (kk == 0) mma_ss_dyn(leader, tmem + kColDK, dqmn, 0, desc_ds, 0, idesc_t, j > 0);
                         else mma_ss<true>(leader, tmem + kColDK, dqmn, kk * 2048, desc_ds, kk * 2048, idesc_t);
                     }
-                    mma_commit(leader, &bars[B_Q_EMPTY0 + g % kQStages]);
-                    mma_commit(leader, &bars[B_PDS_FREE]);
-                    SB_TRACE_EV(m, 0, 3);
-                    if (j + 2 < n) {
-                        issue_sdp(g + 2);
-                        if (ok && j + 3 == n) mma_commit(leader, &bars[B_KV_EMPTY]);
-                    }
+                    mma_commit(leader, &bars[B_Q_EMPTY0 + st]);
                     SB_TRACE_EV(m, 0, 4);
                 }
                 if (!ok) break;
@@ -564,13 +540,14 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
         }
     } else {
-        // ------------------------------------------------------------------ row groups
+        // ------------------------------------------------------------------ row threads: group 0 right half, group 1 left half
         const int grp = warp >> 2;
+        const int hf = grp ^ 1;  // 64-key half of the tile this thread owns
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const float scale = a.inv_temp * kLog2e;
-        uint8_t* prow = sP + r * 128;
-        uint8_t* srow = sDS + r * 128;
+        uint8_t* prow = sP + hf * kQBox + r * 128;
+        uint8_t* srow = sDS + hf * kQBox + r * 128;
         uint32_t G = 0, items = 0;
         bool ok = true;
         SB_TRACE_DECL(c);
@@ -578,17 +555,18 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         int w;
         while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
             const KvWork wk = fetch_kv_work(a, n_items, w);
-            if (!wk.valid) continue;
-            const int n = wk.n_qt - wk.qt0;
+            const int n = wk.n_qt - wk.kt;
+            const int kh = 2 * wk.kt + hf;
+            const bool half_ok = kh * kBK < wk.len;  // the half may lie beyond the end of the sequence
             const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             const float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
-            // per-row scalars of a step (carry of W, prefix of g, drem): loaded one step of this group ahead
+            // per-row scalars of a step (carry of W, prefix of g, drem): loaded one step ahead
             float nW = 0.f, nC = 0.f, nD = 0.f;
             auto load_scalars = [&](int i) {
                 const int qi = i * kBM + r;
                 nW = 0.f; nC = 0.f; nD = 0.f;
-                if (i < wk.n_qt && qi < wk.len) {
-                    const int64_t slot = carry_slot(wk.slot_base, i, wk.kh) * kTileQ;
+                if (half_ok && i < wk.n_qt && qi < wk.len) {
+                    const int64_t slot = carry_slot(wk.slot_base, i, kh) * kTileQ;
                     nW = cw[slot];
                     nC = cc[slot];
                     const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh +
@@ -596,44 +574,40 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     nD = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
                 }
             };
-            load_scalars(wk.qt0 + grp);
-            for (int j = grp; j < n; j += 2) {
-                const int i = wk.qt0 + j;
-                const uint32_t g = G + j, buf = g % kSdpBufs;
+            load_scalars(wk.kt);
+            for (int j = 0; j < n; ++j) {
+                const int i = wk.kt + j;
+                const uint32_t g = G + j;
                 const int qi = i * kBM + r;
                 float W = nW;
                 const float cright = nC, drem = nD;
-                load_scalars(i + 2);
+                load_scalars(i + 1);
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 1);
-                ok = mbar_wait(&bars[B_SDP_READY0 + buf], (g / kSdpBufs) & 1, abort_flag);
+                ok = mbar_wait(&bars[B_SDP_READY], g & 1, abort_flag);
                 if (!ok) break;
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 2);
                 tc_fence_after();
-                const bool masked = i == wk.qt0;
-                const int lim = min(kBK, max(0, qi - wk.kh * kBK + a.attend_current));
+                const bool masked = i == wk.kt;
+                const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
                 uint32_t pp[32], ps[32];
                 float sfx = 0.f;
                 {
                     uint32_t s[32], dp[32];
-                    tmem_ld32(lane_base + kColS + 64 * buf + 32, s);
-                    tmem_ld32(lane_base + kColDP + 64 * buf + 32, dp);
+                    tmem_ld32(lane_base + kColS + 64 * hf + 32, s);
+                    tmem_ld32(lane_base + kColDP + 64 * hf + 32, dp);
                     tmem_wait_ld();
                     if (masked) kv_chunk<true, kF16>(s, dp, scale, 32, lim, drem, cright, W, sfx, pp + 16, ps + 16);
                     else kv_chunk<false, kF16>(s, dp, scale, 32, lim, drem, cright, W, sfx, pp + 16, ps + 16);
-                    tmem_ld32(lane_base + kColS + 64 * buf, s);
-                    tmem_ld32(lane_base + kColDP + 64 * buf, dp);
+                    tmem_ld32(lane_base + kColS + 64 * hf, s);
+                    tmem_ld32(lane_base + kColDP + 64 * hf, dp);
                     tmem_wait_ld();
                     if (masked) kv_chunk<true, kF16>(s, dp, scale, 0, lim, drem, cright, W, sfx, pp, ps);
                     else kv_chunk<false, kF16>(s, dp, scale, 0, lim, drem, cright, W, sfx, pp, ps);
                 }
                 tc_fence_before();
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 3);
-                // the p / ds tiles of the previous step must have been consumed by its dv^T, dk^T
-                if (g > 0) {
-                    ok = mbar_wait(&bars[B_PDS_FREE], (g - 1) & 1, abort_flag);
-                    if (!ok) break;
-                }
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 4);
+                // S / dP of this step became ready only after dv^T, dk^T of the previous one had completed (they were
+                // issued earlier by the same thread), so the p / ds tiles in shared memory are free to overwrite
 #pragma unroll
                 for (int ch = 0; ch < 8; ++ch) {
                     const int off = (ch ^ (r & 7)) << 4;
@@ -642,30 +616,30 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 fence_async_smem();
                 mbar_arrive(&bars[B_PDS_READY]);
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 5);
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 4);
             }
             if (!ok) break;
-            // epilogue: group 0 stores dk, group 1 dv; a thread holds one head-dim index d, the 64 keys along the columns
+            // epilogue: group 0 stores dk, group 1 dv; a thread holds one head-dim index d, the 128 keys along the columns
             ok = mbar_wait(&bars[B_DKV_READY], items & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const int d = D == 128 ? r : ((warp & 3) * 16 + lane);
             const bool d_ok = D == 128 ? true : lane < 16;
-            const int keys_valid = min(kBK, wk.len - wk.kh * kBK);
+            const int keys_valid = min(kKT, wk.len - wk.kt * kKT);
             {
                 const MatView& m = grp == 0 ? a.dk : a.dv;
                 const float sc = grp == 0 ? a.inv_temp : 1.f;
                 char* base = m.ptr + 2 * ((int64_t)wk.b * m.sb + (int64_t)wk.h * m.sh +
-                                          (int64_t)(wk.start + wk.kh * kBK) * m.st + d);
+                                          (int64_t)(wk.start + wk.kt * kKT) * m.st + d);
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
+                for (int q4 = 0; q4 < 4; ++q4) {
                     uint32_t v[32];
-                    tmem_ld32(lane_base + (grp == 0 ? kColDK : kColDV) + half * 32, v);
+                    tmem_ld32(lane_base + (grp == 0 ? kColDK : kColDV) + q4 * 32, v);
                     tmem_wait_ld();
                     if (d_ok) {
 #pragma unroll
                         for (int jj = 0; jj < 32; ++jj) {
-                            const int key = half * 32 + jj;
+                            const int key = q4 * 32 + jj;
                             if (key < keys_valid) {
                                 const float x = __uint_as_float(v[jj]) * sc;
                                 char* ptr = base + 2 * (int64_t)key * m.st;
@@ -696,9 +670,13 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         encode_tile_map(&mk, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBK) ||
         encode_tile_map(&mv, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBK))
         return 1;
-    // both kernels: 2 x (128 x D) + 3 x (64 x D) 16-bit tiles (dq: q, do, 2 k stages, v; dk/dv: k, v, q, do, p, ds)
+    CUtensorMap mk128, mv128;  // the dk/dv kernel loads K and V as 128-row tiles
+    if (encode_tile_map(&mk128, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBM) ||
+        encode_tile_map(&mv128, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBM))
+        return 1;
+    // dq kernel: 2 x (128 x D) + 3 x (64 x D) 16-bit tiles (q, do, 2 k stages, v); dk/dv kernel: k, v, 2 q stages, do, p, ds
     constexpr int need = 2 * kBM * D * 2 + 3 * kBK * D * 2 + 256;
-    constexpr int need_b = (kQStages + kDoStages) * kBM * D * 2 + 2 * kBK * D * 2 + 2 * 128 * 128 + 512;
+    constexpr int need_b = 5 * kBM * D * 2 + 2 * 2 * 128 * 128 + 512;
     // at least 80 KB so that never more than two blocks (2 x 256 tensor-memory columns) share an SM
     constexpr int smem_a = need > 81920 ? need : 81920;
     constexpr int smem_b = need_b > 120 * 1024 ? need_b : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
@@ -712,7 +690,7 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     if (p.bwd_phases != SBATTN_BWD_DKDV) tc_bwd_dq_kernel<D, kF16><<<grid, kThreads, smem_a, st>>>(mq, mk, mv, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk, mv, mdo, a);
+    if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, a);
     return (int)cudaGetLastError();
 }
 
