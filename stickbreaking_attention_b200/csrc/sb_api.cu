@@ -145,6 +145,7 @@ extern "C" int sbattn_bwd(const SbParams* p) {
     if (path < 0) return path;
     cudaStream_t st = (cudaStream_t)p->stream;
     const KArgs a = make_args(*p, L);
+    if (p->bwd_phases == SBATTN_BWD_ALL && launch_zero_tail(*p, a, st) != 0) return SBATTN_ECUDA;
     const int e = path == 1 ? launch_tensor_bwd(*p, L, a, st) : launch_simt_bwd(*p, L, a, st);
     return e == 0 ? SBATTN_OK : SBATTN_ECUDA;
 }

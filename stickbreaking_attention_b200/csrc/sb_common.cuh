@@ -32,7 +32,8 @@ struct WsHeader {
     // work counters of the persistent kernels (forward, backward dq, backward dk/dv): [2k] next work index,
     // [2k+1] blocks that have finished; zeroed by the prep kernel, reset by the last block of every launch
     int32_t sched[8];
-    int32_t pad[52];
+    int32_t covered_end;  // packed layout: end of the last sequence (tokens beyond it belong to no sequence)
+    int32_t pad[51];
 };
 static_assert(sizeof(WsHeader) == 256, "header is one 256-byte line");
 
@@ -126,6 +127,7 @@ template <> __device__ inline __half from_f32<__half>(float x) { return __float2
 
 // launchers implemented in the .cu files (each returns a cudaError_t as int)
 int launch_prep(const SbParams& p, const WsLayout& L, cudaStream_t st);
+int launch_zero_tail(const SbParams& p, const KArgs& a, cudaStream_t st);
 int launch_simt_fwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
 int launch_simt_bwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
 bool tensor_path_eligible(const SbParams& p, bool backward, int* why);

@@ -94,6 +94,7 @@ prep_kernel(WsHeader* hdr, SeqInfo* seqs, int2* items, int32_t* bins, const void
         hdr->n_seqs = n_seqs;
         hdr->total_slots = slot_carry;
         hdr->bad = bad ? 1 : 0;
+        hdr->covered_end = batch > 0 ? tokens : (n_seqs > 0 && !bad ? (int)read_end(cu, cu_width, n_seqs - 1) : 0);
         if (bad) atomicOr(status, SBATTN_ST_BAD_SEQLENS);
     }
     __syncthreads();
@@ -107,7 +108,37 @@ prep_kernel(WsHeader* hdr, SeqInfo* seqs, int2* items, int32_t* bins, const void
     }
 }
 
+// Gradient rows of tokens that belong to no sequence (a pack whose last end is below T) are zero; every other row is
+// written by the backward kernels, so the caller does not have to clear dq, dk, dv beforehand.
+template <typename T>
+__global__ void zero_tail_kernel(const WsHeader* hdr, MatView dq, MatView dk, MatView dv, int heads, int tokens, int D) {
+    const int first = hdr->covered_end;
+    const int rows = tokens - first;
+    if (rows <= 0) return;
+    const int64_t total = (int64_t)rows * heads * D;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int d = (int)(i % D);
+        const int64_t rh = i / D;
+        const int h = (int)(rh % heads);
+        const int64_t t = first + rh / heads;
+        ((T*)dq.ptr)[h * dq.sh + t * dq.st + d] = T(0.f);
+        ((T*)dk.ptr)[h * dk.sh + t * dk.st + d] = T(0.f);
+        ((T*)dv.ptr)[h * dv.sh + t * dv.st + d] = T(0.f);
+    }
+}
+
 }  // namespace
+
+int launch_zero_tail(const SbParams& p, const KArgs& a, cudaStream_t st) {
+    if (p.batch > 0) return 0;  // the batched layout covers every token
+    if (p.dtype == SBATTN_F32)
+        zero_tail_kernel<float><<<64, 256, 0, st>>>(a.hdr, a.dq, a.dk, a.dv, p.heads, p.tokens, p.head_dim);
+    else if (p.dtype == SBATTN_F16)
+        zero_tail_kernel<__half><<<64, 256, 0, st>>>(a.hdr, a.dq, a.dk, a.dv, p.heads, p.tokens, p.head_dim);
+    else
+        zero_tail_kernel<__nv_bfloat16><<<64, 256, 0, st>>>(a.hdr, a.dq, a.dk, a.dv, p.heads, p.tokens, p.head_dim);
+    return (int)cudaGetLastError();
+}
 
 int launch_prep(const SbParams& p, const WsLayout& L, cudaStream_t st) {
     char* ws = (char*)p.fwd_workspace;

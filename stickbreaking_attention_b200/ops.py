@@ -178,9 +178,10 @@ def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale
         if out is not None:
             dq, dk, dv = out
         else:
-            dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+            # no zero-fill: the library writes every row (rows outside all sequences are cleared by a small kernel)
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
             if dq.stride(-1) != 1:
-                dq, dk, dv = (torch.zeros(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
+                dq, dk, dv = (torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
         p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, True)
         p.bwd_phases = phases
         fwd_bytes, bwd_bytes = _workspace_sizes(p)

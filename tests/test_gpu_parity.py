@@ -203,3 +203,22 @@ def test_empty_and_no_grad():
     with torch.no_grad():
         o, rem = sb_attn_varlen(q, q, q, torch.tensor([0, 130], device="cuda"), 130)
     assert torch.isfinite(o.float()).all()
+
+
+def test_tokens_outside_all_sequences_get_zero_gradients():
+    """A pack whose last end is below T: the uncovered rows of dq, dk, dv are zero and covered rows are unaffected."""
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    H, T, D = 2, 400, 64
+    lengths = [150, 130]  # 280 of 400 tokens covered
+    q, k, v, do, drem = [rounded(x, torch.bfloat16) for x in synth(H, T, D, seed=31)]
+    tq, tk, tv = (torch.from_numpy(x).cuda().bfloat16().requires_grad_() for x in (q, k, v))
+    cu = torch.tensor(np.cumsum(lengths), device="cuda")
+    o, rem = sb_attn_varlen(tq, tk, tv, cu, max(lengths), zero_start=False)
+    dq, dk, dv = torch.autograd.grad([o[:, :280], rem[:, :280]], [tq, tk, tv],
+                                     [torch.from_numpy(do[:, :280]).cuda().bfloat16(),
+                                      torch.from_numpy(drem[:, :280]).cuda().bfloat16()])
+    for g in (dq, dk, dv):
+        assert torch.all(g[:, 280:] == 0)
+    want = oracle_varlen(q[:, :280], k[:, :280], v[:, :280], do[:, :280], drem[:, :280], lengths, 1 / math.sqrt(D), False)
+    got = [x.detach().double().cpu().numpy()[:, :280] for x in (o, rem, dq, dk, dv)]
+    assert_close(NAMES, got, want, TOL_BF16)
