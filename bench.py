@@ -31,6 +31,9 @@ if ROOT not in sys.path:
 import numpy as np
 import torch
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in profiles/tc_kernels_c2.md
+NCU_TRAFFIC_BYTES = {"c2-varlen-h32-d128-t16384": {"fwd": 570e6, "bwd_dq": 781e6, "bwd_dkdv": 893e6}}
+
 METRIC = "fwd+bwd TFLOP/s (varlen, bf16)"
 UNIT = "TFLOP/s"
 NOMINAL_BF16_TFLOPS = 2250.0
@@ -371,7 +374,8 @@ def run_ours(args, wl):
         roofline = {
             "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak, "peak_source": f"of {peaks['source']} (burst cuBLAS bf16)",
-            "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS, "traffic": None,
+            "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS,
+            "traffic": (NCU_TRAFFIC_BYTES.get(wl["name"], {}).get(dom) if world == 1 else None), "traffic_unit": "bytes",
             "kernel_ms": kernels,
             "kernel_tflops": {kk: fl_rank * share[kk] / (vv * 1e-3) / 1e12 for kk, vv in kernels.items()},
         }
