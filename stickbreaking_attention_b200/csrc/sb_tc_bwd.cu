@@ -30,13 +30,19 @@ constexpr uint32_t kTmemCols = 256;
 constexpr int kQBox = 128 * 128;  // bytes of one TMA box of a 128-row tile (64 elements wide)
 constexpr int kKBox = 64 * 128;   // bytes of one TMA box of a 64-row tile
 
-// element-wise core shared by both kernels: one score -> (1 - beta), beta
+// Element-wise core shared by both kernels, two adjacent scores at a time so that the operations without a
+// dependency along the row (scaling, 1 + e, 1 - om, dP - drem, p * dA) are packed fp32x2 instructions:
+// om = 1 - beta = 1 / (1 + 2^(s * scale)), masked keys get om = 1 (no stick broken, weight 0).
 template <bool kMasked>
-__device__ __forceinline__ void stick(float s, float scale, int col, int lim, float& om, float& beta) {
-    const float e = ex2_approx(s * scale);
-    om = rcp_approx(1.f + e);
-    beta = 1.f - om;
-    if (kMasked && col >= lim) { om = 1.f; beta = 0.f; }
+__device__ __forceinline__ void stick2(float s0, float s1, float scale, int col, int lim, float2& om, float2& beta) {
+    const float2 x = __fmul2_rn(make_float2(s0, s1), make_float2(scale, scale));
+    const float2 d = __fadd2_rn(make_float2(ex2_approx(x.x), ex2_approx(x.y)), make_float2(1.f, 1.f));
+    om = make_float2(rcp_approx(d.x), rcp_approx(d.y));
+    if (kMasked) {
+        if (col >= lim) om.x = 1.f;
+        if (col + 1 >= lim) om.y = 1.f;
+    }
+    beta = __ffma2_rn(om, make_float2(-1.f, -1.f), make_float2(1.f, 1.f));
 }
 
 // ================================================================================================ dq kernel
@@ -46,15 +52,21 @@ enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_EMPTY0, A_K_EMPT
 template <bool kMasked>
 __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[32], float scale, int col0, int lim,
                                               float drem, float& W) {
-    // right to left: s <- beta, dp <- g = p * (dP - drem)
+    // right to left: s <- beta, dp <- g = p * (dP - drem), with p = W * beta = W - W * om
 #pragma unroll
-    for (int j = 31; j >= 0; --j) {
-        float om, beta;
-        stick<kMasked>(__uint_as_float(s[j]), scale, col0 + j, lim, om, beta);
-        const float p = beta * W;
-        W *= om;
-        dp[j] = __float_as_uint(p * (__uint_as_float(dp[j]) - drem));
-        s[j] = __float_as_uint(beta);
+    for (int jj = 15; jj >= 0; --jj) {
+        float2 om, beta;
+        stick2<kMasked>(__uint_as_float(s[2 * jj]), __uint_as_float(s[2 * jj + 1]), scale, col0 + 2 * jj, lim, om, beta);
+        const float2 t = __fadd2_rn(make_float2(__uint_as_float(dp[2 * jj]), __uint_as_float(dp[2 * jj + 1])),
+                                    make_float2(-drem, -drem));
+        const float w1 = W * om.y, p1 = W - w1;
+        const float w0 = w1 * om.x, p0 = w1 - w0;
+        W = w0;
+        const float2 g = __fmul2_rn(make_float2(p0, p1), t);
+        dp[2 * jj] = __float_as_uint(g.x);
+        dp[2 * jj + 1] = __float_as_uint(g.y);
+        s[2 * jj] = __float_as_uint(beta.x);
+        s[2 * jj + 1] = __float_as_uint(beta.y);
     }
 }
 template <bool kF16>
@@ -347,23 +359,25 @@ __device__ __forceinline__ KvWork fetch_kv_work(const KArgs& a, int n_items, int
 
 template <bool kMasked, bool kF16>
 __device__ __forceinline__ void kv_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], float scale, int col0, int lim,
-                                         float drem, float cright, float& W, float& sfx, uint32_t* pp, uint32_t* ps) {
-    // right to left over 32 columns: p and ds = g - beta * (cright - sum of g to the right)
-    float p[32], ds[32];
+                                         float drem, float& c, float& W, uint32_t* pp, uint32_t* ps) {
+    // right to left over 32 columns, two at a time: p = W * beta = W - W * om and ds = g - beta * c, where c enters as
+    // the inclusive prefix of g at the chunk's right edge and loses every g it passes
 #pragma unroll
-    for (int j = 31; j >= 0; --j) {
-        float om, beta;
-        stick<kMasked>(__uint_as_float(s[j]), scale, col0 + j, lim, om, beta);
-        p[j] = beta * W;
-        W *= om;
-        const float g = p[j] * (__uint_as_float(dp[j]) - drem);
-        ds[j] = g - beta * (cright - sfx);
-        sfx += g;
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        pp[j] = pack16<kF16>(p[2 * j], p[2 * j + 1]);
-        ps[j] = pack16<kF16>(ds[2 * j], ds[2 * j + 1]);
+    for (int jj = 15; jj >= 0; --jj) {
+        float2 om, beta;
+        stick2<kMasked>(__uint_as_float(s[2 * jj]), __uint_as_float(s[2 * jj + 1]), scale, col0 + 2 * jj, lim, om, beta);
+        const float2 t = __fadd2_rn(make_float2(__uint_as_float(dp[2 * jj]), __uint_as_float(dp[2 * jj + 1])),
+                                    make_float2(-drem, -drem));
+        const float w1 = W * om.y, p1 = W - w1;
+        const float w0 = w1 * om.x, p0 = w1 - w0;
+        W = w0;
+        const float2 g = __fmul2_rn(make_float2(p0, p1), t);
+        const float ds1 = fmaf(-beta.y, c, g.y);
+        c -= g.y;
+        const float ds0 = fmaf(-beta.x, c, g.x);
+        c -= g.x;
+        pp[jj] = pack16<kF16>(p0, p1);
+        ps[jj] = pack16<kF16>(ds0, ds1);
     }
 }
 
@@ -590,19 +604,19 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const bool masked = i == wk.kt;
                 const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
                 uint32_t pp[32], ps[32];
-                float sfx = 0.f;
+                float c = cright;  // prefix of g through the right edge of this half; loses every g it passes
                 {
                     uint32_t s[32], dp[32];
                     tmem_ld32(lane_base + kColS + 64 * hf + 32, s);
                     tmem_ld32(lane_base + kColDP + 64 * hf + 32, dp);
                     tmem_wait_ld();
-                    if (masked) kv_chunk<true, kF16>(s, dp, scale, 32, lim, drem, cright, W, sfx, pp + 16, ps + 16);
-                    else kv_chunk<false, kF16>(s, dp, scale, 32, lim, drem, cright, W, sfx, pp + 16, ps + 16);
+                    if (masked) kv_chunk<true, kF16>(s, dp, scale, 32, lim, drem, c, W, pp + 16, ps + 16);
+                    else kv_chunk<false, kF16>(s, dp, scale, 32, lim, drem, c, W, pp + 16, ps + 16);
                     tmem_ld32(lane_base + kColS + 64 * hf, s);
                     tmem_ld32(lane_base + kColDP + 64 * hf, dp);
                     tmem_wait_ld();
-                    if (masked) kv_chunk<true, kF16>(s, dp, scale, 0, lim, drem, cright, W, sfx, pp, ps);
-                    else kv_chunk<false, kF16>(s, dp, scale, 0, lim, drem, cright, W, sfx, pp, ps);
+                    if (masked) kv_chunk<true, kF16>(s, dp, scale, 0, lim, drem, c, W, pp, ps);
+                    else kv_chunk<false, kF16>(s, dp, scale, 0, lim, drem, c, W, pp, ps);
                 }
                 tc_fence_before();
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 3);

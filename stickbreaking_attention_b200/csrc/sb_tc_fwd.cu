@@ -51,14 +51,18 @@ __device__ __forceinline__ void fwd_sweep(uint32_t (&s)[32], float scale, int co
 #pragma unroll
     for (int g = 0; g < 4; ++g) run[g] = 1.f;
 #pragma unroll
-    for (int m = 0; m < 8; ++m) {
+    for (int m = 0; m < 8; m += 2) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-            const int idx = g * 8 + m;
-            float e = ex2_approx(fminf(__uint_as_float(s[idx]) * scale, 15.f));
-            if (kMasked && col0 + idx >= lim) e = 0.f;
-            s[idx] = __float_as_uint(e * run[g]);
-            run[g] = fmaf(run[g], e, run[g]);
+            const int idx = g * 8 + m;  // two adjacent keys: the scaling is one packed fp32x2 multiply
+            const float2 x = __fmul2_rn(make_float2(__uint_as_float(s[idx]), __uint_as_float(s[idx + 1])), make_float2(scale, scale));
+            float e0 = ex2_approx(fminf(x.x, 15.f)), e1 = ex2_approx(fminf(x.y, 15.f));
+            if (kMasked && col0 + idx >= lim) e0 = 0.f;
+            if (kMasked && col0 + idx + 1 >= lim) e1 = 0.f;
+            s[idx] = __float_as_uint(e0 * run[g]);
+            run[g] = fmaf(run[g], e0, run[g]);
+            s[idx + 1] = __float_as_uint(e1 * run[g]);
+            run[g] = fmaf(run[g], e1, run[g]);
         }
     }
 }
@@ -75,7 +79,8 @@ __device__ __forceinline__ void fwd_finish(const uint32_t (&s)[32], const float*
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
         const float fj = f[j >> 2] * mul;
-        packed[j] = pack16<kF16>(__uint_as_float(s[2 * j]) * fj, __uint_as_float(s[2 * j + 1]) * fj);
+        const float2 p = __fmul2_rn(make_float2(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1])), make_float2(fj, fj));
+        packed[j] = pack16<kF16>(p.x, p.y);
     }
 }
 
