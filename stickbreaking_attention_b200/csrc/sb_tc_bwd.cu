@@ -8,13 +8,13 @@
 //                 tile need the product W of (1 - beta) over everything to its right: the forward saved that value
 //                 for every 64-key boundary (carry_w).  The kernel leaves the prefix of g through the right edge
 //                 of every tile in carry_c for the second kernel.
-//   dk/dv kernel  one work item = (head, sequence, 64-key tile), kept stationary; walks the 128-row query tiles
-//                 below it.  Every (query tile, key tile) pair is entered directly with carry_w and carry_c, the
+//   dk/dv kernel  one work item = (head, sequence, 128-key tile), kept stationary; walks the 128-row query tiles
+//                 below it.  Every (query tile, 64-key half) pair is entered directly with carry_w and carry_c, the
 //                 weights and ds are recomputed, written to shared memory as 16-bit operands, and
 //                 dv^T += do^T p, dk^T += q^T ds accumulate in tensor memory for the whole walk; stored once.
 //
-// Both kernels: 192 threads (warps 0-3: one thread per query row; warp 4: TMA; warp 5: tcgen05.mma), two
-// blocks per SM (256 tensor-memory columns each), persistent over the item table.
+// Both kernels: one persistent block per SM with 352 threads (warps 0-7: two groups of one thread per query row,
+// warps 8 and 10: TMA producers, warp 9: tcgen05.mma), all 512 tensor-memory columns, work drawn from a global counter.
 #include "sb_tc_common.cuh"
 
 namespace sb {
@@ -23,10 +23,8 @@ using namespace sm100;
 
 namespace {
 
-constexpr int kThreads = 192;
 constexpr int kBM = 128;  // query rows per tile
 constexpr int kBK = 64;   // keys per tile
-constexpr uint32_t kTmemCols = 256;
 constexpr int kQBox = 128 * 128;  // bytes of one TMA box of a 128-row tile (64 elements wide)
 constexpr int kKBox = 64 * 128;   // bytes of one TMA box of a 64-row tile
 
@@ -46,8 +44,21 @@ __device__ __forceinline__ void stick2(float s0, float s1, float scale, int col,
 }
 
 // ================================================================================================ dq kernel
-enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_EMPTY0, A_K_EMPTY1, A_V_FULL, A_V_EMPTY, A_SDP_READY,
-             A_DS_READY, A_DQ_READY, A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1, kNumDqBars };
+// One block per SM (352 threads), one work item = (head, sequence, 128-row query tile) at a time.  Warps 0-3 / 4-7 are
+// two row groups that take the 64-key tiles of the item in turn, left to right; S and dP live in three buffer pairs in
+// tensor memory, so while the groups work on tiles j and j+1 the tensor cores run dQ += dS K of tile j-1 and S, dP of
+// tile j+2 (with two pairs the next S, dP would have to wait for the dQ contraction that reads dS out of the same columns).
+// The weights of a tile are entered with the forward's carry (carry_w); the prefix of g that ds needs travels from
+// group to group through shared memory: a thread first computes a = g - beta * (prefix inside the tile), then receives
+// the prefix at the tile's left edge from its partner thread in the other group, passes its own on, and finishes
+// ds = a - beta * prefix.  Warp 8 loads Q, dO (once per item) and the K tiles (four-stage ring: a K tile is needed for S
+// early and for dQ late), warp 10 the V tiles, warp 9 issues every tcgen05.mma.
+constexpr int kDqThreads = 352;
+constexpr int kDqKStages = 4, kDqVStages = 3;
+enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_FULL2, A_K_FULL3, A_K_EMPTY0, A_K_EMPTY1, A_K_EMPTY2, A_K_EMPTY3,
+             A_V_FULL0, A_V_FULL1, A_V_FULL2, A_V_EMPTY0, A_V_EMPTY1, A_V_EMPTY2, A_SDP_READY0, A_SDP_READY1, A_SDP_READY2,
+             A_DS_READY0, A_DS_READY1, A_DS_READY2, A_X_C0, A_X_C1, A_DQ_READY, A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1,
+             kNumDqBars };
 
 template <bool kMasked>
 __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[32], float scale, int col0, int lim,
@@ -69,50 +80,63 @@ __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[
         s[2 * jj + 1] = __float_as_uint(beta.y);
     }
 }
-template <bool kF16>
-__device__ __forceinline__ void dq_half_pass2(const uint32_t (&beta)[32], const uint32_t (&g)[32], float& c,
-                                              uint32_t (&packed)[16]) {
-    // left to right: ds = g - beta * (inclusive prefix of g)
-    float ds[32];
+// left to right: g <- a = g - beta * (inclusive prefix of g inside the tile); c carries the running prefix
+__device__ __forceinline__ void dq_half_local(const uint32_t (&beta)[32], uint32_t (&g)[32], float& c) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
         c += __uint_as_float(g[j]);
-        ds[j] = __uint_as_float(g[j]) - __uint_as_float(beta[j]) * c;
+        g[j] = __float_as_uint(fmaf(-__uint_as_float(beta[j]), c, __uint_as_float(g[j])));
     }
+}
+// ds = a - beta * (prefix at the tile's left edge), packed to 16 bits
+template <bool kF16>
+__device__ __forceinline__ void dq_half_finish(const uint32_t (&beta)[32], const uint32_t (&av)[32], float c_in, uint32_t (&packed)[16]) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) packed[j] = pack16<kF16>(ds[2 * j], ds[2 * j + 1]);
+    for (int j = 0; j < 16; ++j) {
+        const float2 ds = __ffma2_rn(make_float2(__uint_as_float(beta[2 * j]), __uint_as_float(beta[2 * j + 1])),
+                                     make_float2(-c_in, -c_in),
+                                     make_float2(__uint_as_float(av[2 * j]), __uint_as_float(av[2 * j + 1])));
+        packed[j] = pack16<kF16>(ds.x, ds.y);
+    }
 }
 
 template <int D, bool kF16>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kDqThreads, 1)
 tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const KArgs a) {
     constexpr int kBoxes = D / 64;
     constexpr int kQBytes = kBM * D * 2, kKBytes = kBK * D * 2;
-    constexpr uint32_t kColS = 0, kColDP = 64, kColDQ = 128, kColDS = 0;
+    constexpr uint32_t kColS = 0, kColDP = 64, kColDQ = 384;  // S / dP buffer b (of three) at +128*b; dS overwrites the left half of S
+    constexpr uint32_t kCols = 512;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sDO = sQ + kQBytes;
-    uint8_t* sK = sDO + kQBytes;  // two stages
-    uint8_t* sV = sK + 2 * kKBytes;
-    uint64_t* bars = (uint64_t*)(sV + kKBytes);
+    uint8_t* sK = sDO + kQBytes;              // kDqKStages tiles
+    uint8_t* sV = sK + kDqKStages * kKBytes;  // kDqVStages tiles
+    uint64_t* bars = (uint64_t*)(sV + kDqVStages * kKBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumDqBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    SchedRing* ring = (SchedRing*)(tmem_slot + 2);
+    SchedRing<Work>* ring = (SchedRing<Work>*)(tmem_slot + 2);
+    float* xc = (float*)(tmem_slot + 32);  // [group][128 rows]: prefix of g through the tile the group has just finished
+    float* wpre = xc + 256;               // [parity][group][128 rows]: carry_w of a group's next tile, copied asynchronously
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int i = 0; i < kNumDqBars; ++i)
-            mbar_init(&bars[i], (i == A_DS_READY || i == A_DQ_FREE) ? 128
-                                : ((i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) ? kRingConsumers : 1));
+        for (int i = 0; i < kNumDqBars; ++i) {
+            uint32_t cnt = 1;
+            if (i == A_DS_READY0 || i == A_DS_READY1 || i == A_DS_READY2 || i == A_X_C0 || i == A_X_C1) cnt = 128;
+            if (i == A_DQ_FREE) cnt = 256;
+            if (i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) cnt = 258;  // MMA warp (one lane), V producer, 256 row threads
+            mbar_init(&bars[i], cnt);
+        }
         *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
         fence_barrier_init();
     }
-    if (warp == 5) {
-        tmem_alloc(tmem_slot, kTmemCols);
+    if (warp == 9) {
+        tmem_alloc(tmem_slot, kCols);
         tmem_relinquish();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == 8 && lane == 0) {
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
@@ -124,19 +148,22 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t tmem = *tmem_slot;
     const int n_items = a.hdr->n_items;
     const int n_work = *abort_flag ? 0 : n_items * a.heads;
+    // G counts key-tile steps over all items of this block: step G uses K stage G % 4, V stage G % 3 and S/dP buffer
+    // G % 3; a barrier that completes once per use is in phase (use count) & 1.
 
-    if (warp == 4) {
+    if (warp == 8) {
+        // ------------------------------------------------------------------ TMA: Q, dO per item, K ring
         if (lane == 0) {
-            uint32_t ph_qe = 1, ph_ke[2] = {1, 1}, ph_ve = 1;
-            uint32_t kcount = 0;
+            uint32_t G = 0, items = 0;
             bool ok = true;
             SchedProducer sched;
             int w;
-            while (ok && (w = sched.next(a.sched + 2, n_work, ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag)) >= 0) {
-                const Work wk = fetch_work(a, n_items, w);
+            Work wk;
+            const auto fetch = [&](int w_) { return fetch_work(a, n_items, w_); };
+            while (ok && (w = sched.next(a.sched + 2, n_work, ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, fetch, wk)) >= 0) {
                 const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
-                ok = mbar_wait(&bars[A_QDO_EMPTY], ph_qe, abort_flag);
-                ph_qe ^= 1;
+                ok = mbar_wait(&bars[A_QDO_EMPTY], (items & 1) ^ 1, abort_flag);
+                ++items;
                 if (!ok) break;
                 mbar_expect_tx(&bars[A_QDO_FULL], 2 * kQBytes);
 #pragma unroll
@@ -144,27 +171,40 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     tma_load_4d(sQ + bx * kQBox, &map_q, &bars[A_QDO_FULL], bx * 64, wk.start + wk.qt * kBM, wk.h, wk.b);
                     tma_load_4d(sDO + bx * kQBox, &map_do, &bars[A_QDO_FULL], bx * 64, wk.start + wk.qt * kBM, wk.h, wk.b);
                 }
-                for (int kh = 0; kh < n_kh; ++kh, ++kcount) {
-                    const int st = kcount & 1;
-                    const int row = wk.start + kh * kBK;
-                    ok = mbar_wait(&bars[A_K_EMPTY0 + st], ph_ke[st], abort_flag);
-                    ph_ke[st] ^= 1;
+                for (int kh = 0; kh < n_kh; ++kh, ++G) {
+                    const uint32_t st = G % kDqKStages;
+                    ok = mbar_wait(&bars[A_K_EMPTY0 + st], ((G / kDqKStages) & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(&bars[A_K_FULL0 + st], kKBytes);
 #pragma unroll
                     for (int bx = 0; bx < kBoxes; ++bx)
-                        tma_load_4d(sK + st * kKBytes + bx * kKBox, &map_k, &bars[A_K_FULL0 + st], bx * 64, row, wk.h, wk.b);
-                    ok = mbar_wait(&bars[A_V_EMPTY], ph_ve, abort_flag);
-                    ph_ve ^= 1;
-                    if (!ok) break;
-                    mbar_expect_tx(&bars[A_V_FULL], kKBytes);
-#pragma unroll
-                    for (int bx = 0; bx < kBoxes; ++bx)
-                        tma_load_4d(sV + bx * kKBox, &map_v, &bars[A_V_FULL], bx * 64, row, wk.h, wk.b);
+                        tma_load_4d(sK + st * kKBytes + bx * kKBox, &map_k, &bars[A_K_FULL0 + st], bx * 64, wk.start + kh * kBK, wk.h, wk.b);
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 10) {
+        // ------------------------------------------------------------------ TMA: V ring
+        if (lane == 0) {
+            uint32_t G = 0;
+            bool ok = true;
+            SchedConsumer sched;
+            int w;
+            Work wk;
+            while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, wk)) >= 0) {
+                const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
+                for (int kh = 0; kh < n_kh; ++kh, ++G) {
+                    const uint32_t st = G % kDqVStages;
+                    ok = mbar_wait(&bars[A_V_EMPTY0 + st], ((G / kDqVStages) & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(&bars[A_V_FULL0 + st], kKBytes);
+#pragma unroll
+                    for (int bx = 0; bx < kBoxes; ++bx)
+                        tma_load_4d(sV + st * kKBytes + bx * kKBox, &map_v, &bars[A_V_FULL0 + st], bx * 64, wk.start + kh * kBK, wk.h, wk.b);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issuer
         {
             const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
             constexpr uint32_t idesc_s = make_idesc(kBM, kBK, kF16 ? 0 : 1, 0, 0);
@@ -172,74 +212,88 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const SmemDesc desc_q = make_desc(smem_u32(sQ), 0, 1024), desc_do = make_desc(smem_u32(sDO), 0, 1024);
             const SmemDesc desc_k = make_desc(smem_u32(sK), 0, 1024), desc_v = make_desc(smem_u32(sV), 0, 1024);
             const SmemDesc desc_kmn = make_desc(smem_u32(sK), kKBox, 1024);  // K tile as MN-major operand of dQ
-            uint32_t ph_qf = 0, ph_kf[2] = {0, 0}, ph_vf = 0, ph_ds = 0, ph_free = 1;
-            uint32_t kcount = 0;
+            uint32_t G = 0, items = 0;
             bool ok = true;
+            SB_TRACE_DECL(m);
+            auto issue_sdp = [&](uint32_t g, bool last_of_item) {
+                const uint32_t kst = g % kDqKStages, vst = g % kDqVStages, buf = g % 3;
+                const SmemDesc dk = {desc_k.lo + kst * (kKBytes >> 4), desc_k.hi};
+                const SmemDesc dv = {desc_v.lo + vst * (kKBytes >> 4), desc_v.hi};
+                ok = mbar_wait(&bars[A_K_FULL0 + kst], (g / kDqKStages) & 1, abort_flag);
+                if (!ok) return;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
+                    if (k == 0) mma_ss<false>(leader, tmem + kColS + 128 * buf, desc_q, oq, dk, okk, idesc_s);
+                    else mma_ss<true>(leader, tmem + kColS + 128 * buf, desc_q, oq, dk, okk, idesc_s);
+                }
+                ok = mbar_wait(&bars[A_V_FULL0 + vst], (g / kDqVStages) & 1, abort_flag);
+                if (!ok) return;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
+                    if (k == 0) mma_ss<false>(leader, tmem + kColDP + 128 * buf, desc_do, oq, dv, okk, idesc_s);
+                    else mma_ss<true>(leader, tmem + kColDP + 128 * buf, desc_do, oq, dv, okk, idesc_s);
+                }
+                mma_commit(leader, &bars[A_SDP_READY0 + buf]);
+                mma_commit(leader, &bars[A_V_EMPTY0 + vst]);
+                if (last_of_item) mma_commit(leader, &bars[A_QDO_EMPTY]);
+            };
             SchedConsumer sched;
             int w;
-            while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, leader)) >= 0) {
-                const Work wk = fetch_work(a, n_items, w);
-                const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
-                ok = mbar_wait(&bars[A_QDO_FULL], ph_qf, abort_flag);
-                ph_qf ^= 1;
+            Work wk;
+            while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, wk, leader, true)) >= 0) {
+                const int n = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
+                ok = mbar_wait(&bars[A_QDO_FULL], items & 1, abort_flag);
                 if (!ok) break;
-                for (int t = 0; t < n_kh; ++t, ++kcount) {
-                    const int st = kcount & 1;
-                    const SmemDesc dk = {desc_k.lo + st * (kKBytes >> 4), desc_k.hi};
-                    const SmemDesc dkmn = {desc_kmn.lo + st * (kKBytes >> 4), desc_kmn.hi};
-                    ok = mbar_wait(&bars[A_K_FULL0 + st], ph_kf[st], abort_flag);
-                    ph_kf[st] ^= 1;
+                for (int j = 0; ok && j < min(n, 3); ++j) issue_sdp(G + j, j + 1 == n);
+                for (int j = 0; ok && j < n; ++j) {
+                    const uint32_t g = G + j, buf = g % 3, kst = g % kDqKStages;
+                    SB_TRACE_EV(m, 0, 1);
+                    ok = mbar_wait(&bars[A_DS_READY0 + buf], (g / 3) & 1, abort_flag);
                     if (!ok) break;
-                    ok = mbar_wait(&bars[A_V_FULL], ph_vf, abort_flag);
-                    ph_vf ^= 1;
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int k = 0; k < D / 16; ++k) {
-                        const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                        if (k == 0) mma_ss<false>(leader, tmem + kColS, desc_q, oq, dk, okk, idesc_s);
-                        else mma_ss<true>(leader, tmem + kColS, desc_q, oq, dk, okk, idesc_s);
-                    }
-#pragma unroll
-                    for (int k = 0; k < D / 16; ++k) {
-                        const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                        if (k == 0) mma_ss<false>(leader, tmem + kColDP, desc_do, oq, desc_v, okk, idesc_s);
-                        else mma_ss<true>(leader, tmem + kColDP, desc_do, oq, desc_v, okk, idesc_s);
-                    }
-                    mma_commit(leader, &bars[A_SDP_READY]);
-                    mma_commit(leader, &bars[A_V_EMPTY]);
-                    if (t == n_kh - 1) mma_commit(leader, &bars[A_QDO_EMPTY]);
-                    ok = mbar_wait(&bars[A_DS_READY], ph_ds, abort_flag);
-                    ph_ds ^= 1;
-                    if (!ok) break;
-                    if (t == 0) {
-                        ok = mbar_wait(&bars[A_DQ_FREE], ph_free, abort_flag);
-                        ph_free ^= 1;
+                    SB_TRACE_EV(m, 0, 2);
+                    if (j == 0) {  // the previous item's dQ must have been read out
+                        ok = mbar_wait(&bars[A_DQ_FREE], (items & 1) ^ 1, abort_flag);
                         if (!ok) break;
                     }
                     tc_fence_after();
+                    const SmemDesc dkmn = {desc_kmn.lo + kst * (kKBytes >> 4), desc_kmn.hi};
+                    const uint32_t a_ds = tmem + kColS + 128 * buf;
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k) {
-                        if (k == 0) mma_ts_dyn(leader, tmem + kColDQ, tmem + kColDS, dkmn, 0, idesc_dq, t > 0);
-                        else mma_ts<true>(leader, tmem + kColDQ, tmem + kColDS + k * 8, dkmn, k * 2048, idesc_dq);
+                        if (k == 0) mma_ts_dyn(leader, tmem + kColDQ, a_ds, dkmn, 0, idesc_dq, j > 0);
+                        else mma_ts<true>(leader, tmem + kColDQ, a_ds + k * 8, dkmn, k * 2048, idesc_dq);
                     }
-                    mma_commit(leader, &bars[A_K_EMPTY0 + st]);
+                    mma_commit(leader, &bars[A_K_EMPTY0 + kst]);
+                    SB_TRACE_EV(m, 0, 3);
+                    if (j + 3 < n) issue_sdp(g + 3, j + 4 == n);
+                    SB_TRACE_EV(m, 0, 4);
                 }
                 if (!ok) break;
                 mma_commit(leader, &bars[A_DQ_READY]);
+                G += n;
+                ++items;
             }
         }
     } else {
-        const int r = tid;
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        // ------------------------------------------------------------------ row groups
+        const int grp = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const float scale = a.inv_temp * kLog2e;
-        uint32_t ph_sdp = 0, ph_dq = 0;
+        float* x_mine = xc + grp * 128;
+        const float* x_other = xc + (grp ^ 1) * 128;
+        uint32_t G = 0, items = 0, ph_x = 0;
         bool ok = true;
+        SB_TRACE_DECL(c);
         SchedConsumer sched;
         int w;
-        while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag)) >= 0) {
-            const Work wk = fetch_work(a, n_items, w);
-            const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
+        Work wk;
+        while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, wk)) >= 0) {
+            const int n = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
             const int qi = wk.qt * kBM + r;
             const bool row_ok = qi < wk.len;
             const int64_t tok = wk.start + qi;
@@ -250,77 +304,96 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
-            float cprefix = 0.f;
-            float W_next = row_ok ? cw[carry_slot(wk.slot_base, wk.qt, 0) * kTileQ] : 0.f;
-            for (int kh = 0; kh < n_kh; ++kh) {
-                const int64_t slot = carry_slot(wk.slot_base, wk.qt, kh) * kTileQ;
-                float W = W_next;
-                if (row_ok && kh + 1 < n_kh) W_next = cw[slot + kTileQ];  // carry of the next tile: in flight during this one
-                ok = mbar_wait(&bars[A_SDP_READY], ph_sdp, abort_flag);
-                ph_sdp ^= 1;
+            // the carry of a tile is copied to shared memory one tile ahead (cp.async): held in a register it would be
+            // spilled, and the spill store would wait for the load
+            float* wslot = wpre + grp * 128 + r;
+            if (row_ok && grp < n) cp_async4(wslot, cw + carry_slot(wk.slot_base, wk.qt, grp) * kTileQ);
+            for (int j = grp, it = 0; j < n; j += 2, it ^= 1) {
+                const uint32_t g = G + j, buf = g % 3;
+                const int64_t slot = carry_slot(wk.slot_base, wk.qt, j) * kTileQ;
+                cp_async_wait_all();
+                float W = row_ok ? wslot[it * 256] : 0.f;
+                if (row_ok && j + 2 < n) cp_async4(wslot + (it ^ 1) * 256, cw + slot + 2 * kTileQ);
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 1);
+                ok = mbar_wait(&bars[A_SDP_READY0 + buf], (g / 3) & 1, abort_flag);
                 if (!ok) break;
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 2);
                 tc_fence_after();
-                const bool masked = kh >= 2 * wk.qt;  // the tile reaches the diagonal
-                const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
-                uint32_t s[32], dp[32], packed[16];
-                // right half: beta and g go back to tensor memory until the left half has been swept
-                tmem_ld32(lane_base + kColS + 32, s);
-                tmem_ld32(lane_base + kColDP + 32, dp);
+                const bool masked = j >= 2 * wk.qt;  // the tile reaches the diagonal
+                const int lim = min(kBK, max(0, qi - j * kBK + a.attend_current));
+                uint32_t sr[32], gr[32], sl[32], gl[32], packed[16];
+                tmem_ld32(lane_base + kColS + 128 * buf + 32, sr);
+                tmem_ld32(lane_base + kColDP + 128 * buf + 32, gr);
+                tmem_ld32(lane_base + kColS + 128 * buf, sl);
+                tmem_ld32(lane_base + kColDP + 128 * buf, gl);
                 tmem_wait_ld();
-                if (masked) dq_half_pass1<true>(s, dp, scale, 32, lim, drem, W);
-                else dq_half_pass1<false>(s, dp, scale, 32, lim, drem, W);
-                tmem_st32(lane_base + kColS + 32, s);
-                tmem_st32(lane_base + kColDP + 32, dp);
-                // left half
-                tmem_ld32(lane_base + kColS, s);
-                tmem_ld32(lane_base + kColDP, dp);
-                tmem_wait_ld();
-                if (masked) dq_half_pass1<true>(s, dp, scale, 0, lim, drem, W);
-                else dq_half_pass1<false>(s, dp, scale, 0, lim, drem, W);
-                float c = cprefix;
-                dq_half_pass2<kF16>(s, dp, c, packed);
-                tmem_wait_st();
-                tmem_st16(lane_base + kColDS, packed);
-                tmem_ld32(lane_base + kColS + 32, s);
-                tmem_ld32(lane_base + kColDP + 32, dp);
-                tmem_wait_ld();
-                dq_half_pass2<kF16>(s, dp, c, packed);
-                tmem_st16(lane_base + kColDS + 16, packed);
-                cprefix = c;
-                if (row_ok) cc[slot] = c;
+                if (masked) {
+                    dq_half_pass1<true>(sr, gr, scale, 32, lim, drem, W);
+                    dq_half_pass1<true>(sl, gl, scale, 0, lim, drem, W);
+                } else {
+                    dq_half_pass1<false>(sr, gr, scale, 32, lim, drem, W);
+                    dq_half_pass1<false>(sl, gl, scale, 0, lim, drem, W);
+                }
+                float cl = 0.f;  // prefix of g inside the tile
+                dq_half_local(sl, gl, cl);
+                dq_half_local(sr, gr, cl);
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 3);
+                // prefix at the tile's left edge: from the partner thread, which handled the tile to the left
+                float c_in = 0.f;
+                if (j > 0) {
+                    ok = mbar_wait(&bars[A_X_C0 + (grp ^ 1)], ph_x, abort_flag);
+                    ph_x ^= 1;
+                    if (!ok) break;
+                    c_in = x_other[r];
+                }
+                const float c_out = c_in + cl;
+                if (j + 1 < n) {
+                    x_mine[r] = c_out;
+                    mbar_arrive(&bars[A_X_C0 + grp]);
+                }
+                if (row_ok) cc[slot] = c_out;  // prefix through the right edge of this tile, for the dk/dv kernel
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 4);
+                dq_half_finish<kF16>(sl, gl, c_in, packed);
+                tmem_st16(lane_base + kColS + 128 * buf, packed);
+                dq_half_finish<kF16>(sr, gr, c_in, packed);
+                tmem_st16(lane_base + kColS + 128 * buf + 16, packed);
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(&bars[A_DS_READY]);
+                mbar_arrive(&bars[A_DS_READY0 + buf]);
+                if (r == 0) SB_TRACE_EV(c, 1 + grp, 5);
             }
             if (!ok) break;
-            ok = mbar_wait(&bars[A_DQ_READY], ph_dq, abort_flag);
-            ph_dq ^= 1;
+            // epilogue: each group stores half of the head dim of every row
+            ok = mbar_wait(&bars[A_DQ_READY], items & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            char* orow = a.dq.ptr + 2 * ((int64_t)wk.b * a.dq.sb + (int64_t)wk.h * a.dq.sh + tok * a.dq.st);
+            const int d0 = grp * (D / 2);
+            char* orow = a.dq.ptr + 2 * ((int64_t)wk.b * a.dq.sb + (int64_t)wk.h * a.dq.sh + tok * a.dq.st + d0);
 #pragma unroll
-            for (int cidx = 0; cidx < D / 32; ++cidx) {
+            for (int cidx = 0; cidx < D / 64; ++cidx) {
                 uint32_t v[32];
-                tmem_ld32(lane_base + kColDQ + cidx * 32, v);
+                tmem_ld32(lane_base + kColDQ + d0 + cidx * 32, v);
                 tmem_wait_ld();
                 if (row_ok) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
+                    for (int q4 = 0; q4 < 4; ++q4) {
                         uint4 u;
                         uint32_t* up = (uint32_t*)&u;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            up[j] = pack16<kF16>(__uint_as_float(v[g * 8 + 2 * j]) * a.inv_temp,
-                                                 __uint_as_float(v[g * 8 + 2 * j + 1]) * a.inv_temp);
-                        *(uint4*)(orow + (cidx * 32 + g * 8) * 2) = u;
+                        for (int jj = 0; jj < 4; ++jj)
+                            up[jj] = pack16<kF16>(__uint_as_float(v[q4 * 8 + 2 * jj]) * a.inv_temp,
+                                                  __uint_as_float(v[q4 * 8 + 2 * jj + 1]) * a.inv_temp);
+                        *(uint4*)(orow + (cidx * 32 + q4 * 8) * 2) = u;
                     }
                 }
             }
             tc_fence_before();
             mbar_arrive(&bars[A_DQ_FREE]);
+            G += n;
+            ++items;
         }
     }
-    tc_teardown(abort_flag, a.status, tmem, kTmemCols, 5);
+    tc_teardown(abort_flag, a.status, tmem, kCols, 9);
     sched_finish(a.sched + 2);
 }
 
@@ -400,7 +473,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint64_t* bars = (uint64_t*)(sDS + kBufBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumKvBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    SchedRing* ring = (SchedRing*)(tmem_slot + 2);
+    SchedRing<KvWork>* ring = (SchedRing<KvWork>*)(tmem_slot + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -439,8 +512,9 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             bool ok = true;
             SchedProducer sched;
             int w;
-            while (ok && (w = sched.next(a.sched + 4, n_work, ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
-                const KvWork wk = fetch_kv_work(a, n_items, w);
+            KvWork wk;
+            const auto fetch = [&](int w_) { return fetch_kv_work(a, n_items, w_); };
+            while (ok && (w = sched.next(a.sched + 4, n_work, ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, fetch, wk)) >= 0) {
                 ok = mbar_wait(&bars[B_KV_EMPTY], (items & 1) ^ 1, abort_flag);
                 ++items;
                 if (!ok) break;
@@ -468,8 +542,8 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             bool ok = true;
             SchedConsumer sched;
             int w;
-            while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
-                const KvWork wk = fetch_kv_work(a, n_items, w);
+            KvWork wk;
+            while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk)) >= 0) {
                 for (int i = wk.kt; i < wk.n_qt; ++i, ++G) {
                     ok = mbar_wait(&bars[B_DO_EMPTY], (G & 1) ^ 1, abort_flag);
                     if (!ok) break;
@@ -495,8 +569,8 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             SB_TRACE_DECL(m);
             SchedConsumer sched;
             int w;
-            while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, leader)) >= 0) {
-                const KvWork wk = fetch_kv_work(a, n_items, w);
+            KvWork wk;
+            while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk, leader, true)) >= 0) {
                 const int n = wk.n_qt - wk.kt;
                 ok = mbar_wait(&bars[B_KV_FULL], items & 1, abort_flag);
                 for (int j = 0; ok && j < n; ++j) {
@@ -567,8 +641,8 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         SB_TRACE_DECL(c);
         SchedConsumer sched;
         int w;
-        while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag)) >= 0) {
-            const KvWork wk = fetch_kv_work(a, n_items, w);
+        KvWork wk;
+        while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk)) >= 0) {
             const int n = wk.n_qt - wk.kt;
             const int kh = 2 * wk.kt + hf;
             const bool half_ok = kh * kBK < wk.len;  // the half may lie beyond the end of the sequence
@@ -689,10 +763,10 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         encode_tile_map(&mv128, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBM))
         return 1;
     // dq kernel: 2 x (128 x D) + 3 x (64 x D) 16-bit tiles (q, do, 2 k stages, v); dk/dv kernel: k, v, 2 q stages, do, p, ds
-    constexpr int need = 2 * kBM * D * 2 + 3 * kBK * D * 2 + 256;
+    constexpr int need = 2 * kBM * D * 2 + (kDqKStages + kDqVStages) * kBK * D * 2 + 4096;
     constexpr int need_b = 5 * kBM * D * 2 + 2 * 2 * 128 * 128 + 512;
     // at least 80 KB so that never more than two blocks (2 x 256 tensor-memory columns) share an SM
-    constexpr int smem_a = need > 81920 ? need : 81920;
+    constexpr int smem_a = need > 120 * 1024 ? need : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
     constexpr int smem_b = need_b > 120 * 1024 ? need_b : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
     cudaError_t e = cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
     if (e != cudaSuccess) return (int)e;
@@ -701,7 +775,7 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     const int grid = 2 * sm_count();
-    if (p.bwd_phases != SBATTN_BWD_DKDV) tc_bwd_dq_kernel<D, kF16><<<grid, kThreads, smem_a, st>>>(mq, mk, mv, mdo, a);
+    if (p.bwd_phases != SBATTN_BWD_DKDV) tc_bwd_dq_kernel<D, kF16><<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk, mv, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, a);

@@ -63,24 +63,31 @@ __device__ __forceinline__ Work fetch_work(const KArgs& a, int n_items, int w) {
 }
 
 // ---------------------------------------------------------------------------------------------- work scheduler
-// One thread of the block (the TMA producer) draws work indices from a global counter and hands them to the MMA
-// thread and the 128 row threads through a two-slot ring in shared memory.  A negative index ends the block.
+// One thread of the block (a TMA producer) draws work indices from a global counter, looks the item up (two dependent
+// global loads) and hands index and item to the other roles through a two-slot ring in shared memory, so that nobody
+// else pays the lookup latency when an item begins.  A negative index ends the block.
 constexpr int kRing = 2;
-constexpr int kRingConsumers = 129;  // 1 MMA thread + 128 row threads
+template <typename T>
 struct SchedRing {
     int32_t slot[kRing];
+    T work[kRing];
 };
 struct SchedProducer {
     int i = 0;
     uint32_t ph[kRing] = {1, 1};
-    __device__ __forceinline__ int next(int32_t* counter, int n_work, SchedRing* ring, uint64_t* full, uint64_t* empty,
-                                        volatile uint32_t* abort_flag) {
+    template <typename T, typename F>
+    __device__ __forceinline__ int next(int32_t* counter, int n_work, SchedRing<T>* ring, uint64_t* full, uint64_t* empty,
+                                        volatile uint32_t* abort_flag, F fetch, T& out) {
         const int sl = i & (kRing - 1);
         ++i;
         if (!sm100::mbar_wait(&empty[sl], ph[sl], abort_flag)) return -1;
         ph[sl] ^= 1;
         int w = atomicAdd(counter, 1);
         if (w >= n_work) w = -1;
+        if (w >= 0) {
+            out = fetch(w);
+            ring->work[sl] = out;
+        }
         ring->slot[sl] = w;
         sm100::mbar_arrive(&full[sl]);
         return w;
@@ -89,14 +96,18 @@ struct SchedProducer {
 struct SchedConsumer {
     int i = 0;
     uint32_t ph[kRing] = {0, 0};
-    // `arrive`: false for all but one lane when a whole warp consumes together (the slot counts one arrival per consumer)
-    __device__ __forceinline__ int next(SchedRing* ring, uint64_t* full, uint64_t* empty, volatile uint32_t* abort_flag,
-                                        bool arrive = true) {
+    // A whole warp that consumes together (the slot counts it as one consumer) passes whole_warp = true and
+    // arrive = true in one lane only.
+    template <typename T>
+    __device__ __forceinline__ int next(SchedRing<T>* ring, uint64_t* full, uint64_t* empty, volatile uint32_t* abort_flag,
+                                        T& out, bool arrive = true, bool whole_warp = false) {
         const int sl = i & (kRing - 1);
         ++i;
         if (!sm100::mbar_wait(&full[sl], ph[sl], abort_flag)) return -1;
         ph[sl] ^= 1;
-        const int w = ((volatile SchedRing*)ring)->slot[sl];
+        const int w = ring->slot[sl];
+        if (w >= 0) out = ring->work[sl];
+        if (whole_warp) __syncwarp();  // every lane has its copy before one of them releases the slot
         if (arrive) sm100::mbar_arrive(&empty[sl]);
         return w;
     }

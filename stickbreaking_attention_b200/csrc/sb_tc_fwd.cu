@@ -97,7 +97,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     uint8_t* sK = sQ + kTileBytes;             // kKStages tiles
     uint8_t* sV = sK + kKStages * kTileBytes;  // kVStages tiles
     uint64_t* bars = (uint64_t*)(sV + kVStages * kTileBytes);
-    SchedRing* ring = (SchedRing*)(bars + kNumBars);
+    SchedRing<Work>* ring = (SchedRing<Work>*)(bars + kNumBars);
     uint32_t* tmem_slot = (uint32_t*)(ring + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* xw = (float*)(tmem_slot + 4);  // [group][128 rows]: carry leaving the tile the group has just swept
@@ -138,8 +138,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             bool ok = true;
             SchedProducer sched;
             int w;
-            while (ok && (w = sched.next(a.sched + 0, n_work, ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
-                const Work wk = fetch_work(a, n_items, w);
+            Work wk;
+            const auto fetch = [&](int w_) { return fetch_work(a, n_items, w_); };
+            while (ok && (w = sched.next(a.sched + 0, n_work, ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag, fetch, wk)) >= 0) {
                 ok = mbar_wait(&bars[Q_EMPTY], ph_qe, abort_flag);
                 ph_qe ^= 1;
                 if (!ok) break;
@@ -168,8 +169,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             bool ok = true;
             SchedConsumer sched;
             int w;
-            while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
-                const Work wk = fetch_work(a, n_items, w);
+            Work wk;
+            while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag, wk)) >= 0) {
                 for (int kt = wk.qt; kt >= 0; --kt, ++kv) {
                     const int st = kv & 1;
                     uint32_t& ph_ve = st ? ph_ve1 : ph_ve0;
@@ -223,8 +224,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             };
             SchedConsumer sched;
             int w;
-            while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag, leader)) >= 0) {
-                const Work wk = fetch_work(a, n_items, w);
+            Work wk;
+            while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag, wk, leader, true)) >= 0) {
                 const int n = wk.qt + 1;
                 ok = mbar_wait(&bars[Q_FULL], ph_qf, abort_flag);
                 ph_qf ^= 1;
@@ -282,8 +283,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         SB_TRACE_DECL(c);
         SchedConsumer sched;
         int w;
-        while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag)) >= 0) {
-            const Work wk = fetch_work(a, n_items, w);
+        Work wk;
+        while (ok && (w = sched.next(ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag, wk)) >= 0) {
             const int n = wk.qt + 1;
             const int qi = wk.qt * kBM + r;
             const bool row_ok = qi < wk.len;
