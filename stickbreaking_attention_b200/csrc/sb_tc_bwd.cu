@@ -28,19 +28,33 @@ constexpr int kBK = 64;   // keys per tile
 constexpr int kQBox = 128 * 128;  // bytes of one TMA box of a 128-row tile (64 elements wide)
 constexpr int kKBox = 64 * 128;   // bytes of one TMA box of a 64-row tile
 
-// Element-wise core shared by both kernels, two adjacent scores at a time so that the operations without a
-// dependency along the row (scaling, 1 + e, 1 - om, dP - drem, p * dA) are packed fp32x2 instructions:
-// om = 1 - beta = 1 / (1 + 2^(s * scale)), masked keys get om = 1 (no stick broken, weight 0).
+// Element-wise core shared by both kernels, four adjacent scores at a time: om = 1 - beta = 1 / (1 + 2^(s * scale));
+// masked keys get om = 1 (no stick broken, weight 0).  The operations without a dependency along the row are packed
+// fp32x2 instructions, and the four reciprocals cost one MUFU operation: with d_i = 1 + e_i,
+// 1 / d_i = (product of the other three) / (d_0 d_1 d_2 d_3).  The exponent is clamped at 30 so that the product of four
+// stays finite (om = 2^-30 instead of something smaller: no visible difference).
 template <bool kMasked>
-__device__ __forceinline__ void stick2(float s0, float s1, float scale, int col, int lim, float2& om, float2& beta) {
-    const float2 x = __fmul2_rn(make_float2(s0, s1), make_float2(scale, scale));
-    const float2 d = __fadd2_rn(make_float2(ex2_approx(x.x), ex2_approx(x.y)), make_float2(1.f, 1.f));
-    om = make_float2(rcp_approx(d.x), rcp_approx(d.y));
+__device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, float scale, int col, int lim, float2& om01,
+                                       float2& om23) {
+    float2 x01 = __fmul2_rn(make_float2(s0, s1), make_float2(scale, scale));
+    float2 x23 = __fmul2_rn(make_float2(s2, s3), make_float2(scale, scale));
+    x01.x = fminf(x01.x, 30.f);
+    x01.y = fminf(x01.y, 30.f);
+    x23.x = fminf(x23.x, 30.f);
+    x23.y = fminf(x23.y, 30.f);
     if (kMasked) {
-        if (col >= lim) om.x = 1.f;
-        if (col + 1 >= lim) om.y = 1.f;
+        if (col >= lim) x01.x = -INFINITY;
+        if (col + 1 >= lim) x01.y = -INFINITY;
+        if (col + 2 >= lim) x23.x = -INFINITY;
+        if (col + 3 >= lim) x23.y = -INFINITY;
     }
-    beta = __ffma2_rn(om, make_float2(-1.f, -1.f), make_float2(1.f, 1.f));
+    const float2 d01 = __fadd2_rn(make_float2(ex2_approx(x01.x), ex2_approx(x01.y)), make_float2(1.f, 1.f));
+    const float2 d23 = __fadd2_rn(make_float2(ex2_approx(x23.x), ex2_approx(x23.y)), make_float2(1.f, 1.f));
+    const float2 m = __fmul2_rn(d01, d23);  // (d0 d2, d1 d3)
+    const float r = rcp_approx(m.x * m.y);
+    const float2 rm = make_float2(r * m.y, r * m.x);  // (1 / (d0 d2), 1 / (d1 d3))
+    om01 = __fmul2_rn(rm, d23);
+    om23 = __fmul2_rn(rm, d01);
 }
 
 // ================================================================================================ dq kernel
@@ -65,19 +79,25 @@ __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[
                                               float drem, float& W) {
     // right to left: s <- beta, dp <- g = p * (dP - drem), with p = W * beta = W - W * om
 #pragma unroll
-    for (int jj = 15; jj >= 0; --jj) {
-        float2 om, beta;
-        stick2<kMasked>(__uint_as_float(s[2 * jj]), __uint_as_float(s[2 * jj + 1]), scale, col0 + 2 * jj, lim, om, beta);
-        const float2 t = __fadd2_rn(make_float2(__uint_as_float(dp[2 * jj]), __uint_as_float(dp[2 * jj + 1])),
-                                    make_float2(-drem, -drem));
-        const float w1 = W * om.y, p1 = W - w1;
-        const float w0 = w1 * om.x, p0 = w1 - w0;
-        W = w0;
-        const float2 g = __fmul2_rn(make_float2(p0, p1), t);
-        dp[2 * jj] = __float_as_uint(g.x);
-        dp[2 * jj + 1] = __float_as_uint(g.y);
-        s[2 * jj] = __float_as_uint(beta.x);
-        s[2 * jj + 1] = __float_as_uint(beta.y);
+    for (int q = 7; q >= 0; --q) {
+        float2 om[2];
+        stick4<kMasked>(__uint_as_float(s[4 * q]), __uint_as_float(s[4 * q + 1]), __uint_as_float(s[4 * q + 2]),
+                        __uint_as_float(s[4 * q + 3]), scale, col0 + 4 * q, lim, om[0], om[1]);
+#pragma unroll
+        for (int h = 1; h >= 0; --h) {
+            const int jj = 2 * q + h;
+            const float2 beta = __ffma2_rn(om[h], make_float2(-1.f, -1.f), make_float2(1.f, 1.f));
+            const float2 t = __fadd2_rn(make_float2(__uint_as_float(dp[2 * jj]), __uint_as_float(dp[2 * jj + 1])),
+                                        make_float2(-drem, -drem));
+            const float w1 = W * om[h].y, p1 = W - w1;
+            const float w0 = w1 * om[h].x, p0 = w1 - w0;
+            W = w0;
+            const float2 g = __fmul2_rn(make_float2(p0, p1), t);
+            dp[2 * jj] = __float_as_uint(g.x);
+            dp[2 * jj + 1] = __float_as_uint(g.y);
+            s[2 * jj] = __float_as_uint(beta.x);
+            s[2 * jj + 1] = __float_as_uint(beta.y);
+        }
     }
 }
 // left to right: g <- a = g - beta * (inclusive prefix of g inside the tile); c carries the running prefix
@@ -398,17 +418,31 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 // ================================================================================================ dk/dv kernel
-// One block per SM (352 threads) keeps a 128-key tile stationary: warps 0-3 own its right 64 keys, warps 4-7 its left
-// 64 keys (one thread per query row in each group; the halves are independent because carry_w / carry_c exist at every
-// 64-key boundary), warp 8 loads K, V (once per item) and the Q tiles (two-stage ring), warp 10 the dO tiles, warp 9
-// issues every tcgen05.mma.  All four contractions run with N = 128, the widest shape the tensor-memory budget allows:
-// S and dP [128 q x 128 keys], dv^T and dk^T [D x 128 keys] (an MMA instruction costs the same ~65 cycles for N = 64 and
-// N = 128, so narrow tiles waste half of the tensor pipe).  dO is released as soon as dv^T has consumed it and Q one
-// tile later than needed for S, which hides most of the TMA latency of the next tile behind dk^T and S.
-constexpr int kKvThreads = 352;
+// One block per SM (384 threads) keeps a 128-key tile stationary and walks the 128-row query tiles below it.  All four
+// contractions run with M = 128 and N = 128 (N = D for the last two), the widest shape the tensor-memory budget
+// allows: S and dP [128 q x 128 keys], dv and dk [128 keys x D] (an MMA instruction costs the same ~65 cycles for N = 64
+// and N = 128, so narrow tiles waste half of the tensor pipe).  Tensor memory is full with these four, so S and dP cannot
+// be double-buffered; the step is pipelined another way:
+//   * a row thread copies its 64 scores and 64 dP values to registers as soon as they exist and releases S / dP at once,
+//     so the tensor cores compute S, dP of the next query tile while the threads work on this one;
+//   * the row threads form two halves by query row (rows 0-63 / 64-127).  dv += p^T do and dk += ds^T q reduce
+//     over query rows, so each half contributes its own four k-steps; the halves share ONE pair of p / ds buffers of
+//     64 rows and take turns, which settles into a stagger of about a third of a step;
+//   * Q and dO are loaded twice from the L2: whole tiles one step early for S, dP (one slot each), and as 64-row halves
+//     just in time for dk, dv (one slot per half).  Holding a tile from its first use to its last would need three
+//     slots per operand, which shared memory does not have;
+//   * the steps of all items form one stream: S, dP of the first step of the next item are computed while the last step
+//     of this one is still being worked on, and dk, dv of a finished item are stored in the middle of the next item's
+//     first step.
+// Inside a half, warps of group 0 own the right 64 keys of the tile and warps of group 1 the left 64 keys (independent,
+// because carry_w / carry_c exist at every 64-key boundary).  Warp 8 loads K, V (once per item) and the early Q, dO
+// tiles, warp 10 the late halves, warp 11 fetches the per-row scalars of the next step (carry_w, carry_c, drem) into
+// shared memory, warp 9 issues every tcgen05.mma.
+constexpr int kKvThreads = 384;
 constexpr int kKT = 128;  // keys per stationary tile
-enum KvBar { B_KV_FULL, B_KV_EMPTY, B_Q_FULL0, B_Q_FULL1, B_Q_EMPTY0, B_Q_EMPTY1, B_DO_FULL, B_DO_EMPTY, B_SDP_READY, B_PDS_READY,
-             B_DKV_READY, B_DKV_FREE, B_WORK_FULL0, B_WORK_FULL1, B_WORK_EMPTY0, B_WORK_EMPTY1, kNumKvBars };
+enum KvBar { B_KV_FULL, B_KV_EMPTY, B_E_FULL, B_E_EMPTY, B_L_FULL0, B_L_FULL1, B_L_EMPTY0, B_L_EMPTY1, B_SDP_READY, B_LOADED,
+             B_PDS_READY0, B_PDS_READY1, B_PDS_FREE0, B_PDS_FREE1, B_SC_FULL, B_DKV_READY, B_DKV_FREE, B_WORK_FULL0,
+             B_WORK_FULL1, B_WORK_EMPTY0, B_WORK_EMPTY1, kNumKvBars };
 
 struct KvWork {
     int h, b, start, len, kt, slot_base, n_qt;
@@ -433,54 +467,97 @@ __device__ __forceinline__ KvWork fetch_kv_work(const KArgs& a, int n_items, int
 template <bool kMasked, bool kF16>
 __device__ __forceinline__ void kv_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], float scale, int col0, int lim,
                                          float drem, float& c, float& W, uint32_t* pp, uint32_t* ps) {
-    // right to left over 32 columns, two at a time: p = W * beta = W - W * om and ds = g - beta * c, where c enters as
+    // right to left over 32 columns: p = W * beta = W - W * om and ds = g - beta * c = om * c - (c - g), where c enters as
     // the inclusive prefix of g at the chunk's right edge and loses every g it passes
 #pragma unroll
-    for (int jj = 15; jj >= 0; --jj) {
-        float2 om, beta;
-        stick2<kMasked>(__uint_as_float(s[2 * jj]), __uint_as_float(s[2 * jj + 1]), scale, col0 + 2 * jj, lim, om, beta);
-        const float2 t = __fadd2_rn(make_float2(__uint_as_float(dp[2 * jj]), __uint_as_float(dp[2 * jj + 1])),
-                                    make_float2(-drem, -drem));
-        const float w1 = W * om.y, p1 = W - w1;
-        const float w0 = w1 * om.x, p0 = w1 - w0;
-        W = w0;
-        const float2 g = __fmul2_rn(make_float2(p0, p1), t);
-        const float ds1 = fmaf(-beta.y, c, g.y);
-        c -= g.y;
-        const float ds0 = fmaf(-beta.x, c, g.x);
-        c -= g.x;
-        pp[jj] = pack16<kF16>(p0, p1);
-        ps[jj] = pack16<kF16>(ds0, ds1);
+    for (int q = 7; q >= 0; --q) {
+        float2 om[2];
+        stick4<kMasked>(__uint_as_float(s[4 * q]), __uint_as_float(s[4 * q + 1]), __uint_as_float(s[4 * q + 2]),
+                        __uint_as_float(s[4 * q + 3]), scale, col0 + 4 * q, lim, om[0], om[1]);
+#pragma unroll
+        for (int h = 1; h >= 0; --h) {
+            const int jj = 2 * q + h;
+            const float2 t = __fadd2_rn(make_float2(__uint_as_float(dp[2 * jj]), __uint_as_float(dp[2 * jj + 1])),
+                                        make_float2(-drem, -drem));
+            const float w1 = W * om[h].y, p1 = W - w1;
+            const float w0 = w1 * om[h].x, p0 = w1 - w0;
+            W = w0;
+            const float2 g = __fmul2_rn(make_float2(p0, p1), t);
+            const float c1 = c - g.y;
+            const float ds1 = fmaf(om[h].y, c, -c1);
+            const float c0 = c1 - g.x;
+            const float ds0 = fmaf(om[h].x, c1, -c0);
+            c = c0;
+            pp[jj] = pack16<kF16>(p0, p1);
+            ps[jj] = pack16<kF16>(ds0, ds1);
+        }
     }
+}
+
+// dk or dv of a finished item out of tensor memory: a thread holds one key row, the head dim along the columns.
+// Not inlined: it runs once per item, and inside the step loop it would only dilute the instruction cache.
+template <int D, bool kF16>
+__device__ __noinline__ void kv_store_rows(const MatView m, float sc, const KvWork e, int r, uint32_t taddr) {
+    tc_fence_after();
+    const bool key_ok = e.kt * kKT + r < e.len;
+    char* orow = m.ptr + 2 * ((int64_t)e.b * m.sb + (int64_t)e.h * m.sh + (int64_t)(e.start + e.kt * kKT + r) * m.st);
+#pragma unroll
+    for (int cidx = 0; cidx < D / 32; ++cidx) {
+        uint32_t v[32];
+        tmem_ld32(taddr + cidx * 32, v);
+        tmem_wait_ld();
+        if (key_ok) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                uint4 u;
+                uint32_t* up = (uint32_t*)&u;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj)
+                    up[jj] = pack16<kF16>(__uint_as_float(v[q4 * 8 + 2 * jj]) * sc, __uint_as_float(v[q4 * 8 + 2 * jj + 1]) * sc);
+                *(uint4*)(orow + (cidx * 32 + q4 * 8) * 2) = u;
+            }
+        }
+    }
+    tc_fence_before();
 }
 
 template <int D, bool kF16>
 __global__ void __launch_bounds__(kKvThreads, 1)
 tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const KArgs a) {
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                   const __grid_constant__ CUtensorMap map_q64, const __grid_constant__ CUtensorMap map_do64, const KArgs a) {
     constexpr int kBoxes = D / 64;
     constexpr int kQBytes = kBM * D * 2;     // a 128-row tile of Q, dO, K or V
-    constexpr int kBufBytes = 2 * 128 * 128;  // 128 query rows x 128 keys, 16-bit, as two 64-key blocks
+    constexpr int kHalfBytes = kQBytes / 2;  // 64 rows of Q or dO: kBoxes boxes of kKBox bytes
+    constexpr int kBufBytes = 2 * 64 * 128;  // 64 query rows x 128 keys, 16-bit, as two 64-key blocks
     constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 384;
     constexpr uint32_t kCols = 512;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;
     uint8_t* sV = sK + kQBytes;
-    uint8_t* sQ = sV + kQBytes;          // two stages
-    uint8_t* sDO = sQ + 2 * kQBytes;
-    uint8_t* sP = sDO + kQBytes;
+    uint8_t* sQe = sV + kQBytes;     // Q of the step whose S is computed next
+    uint8_t* sDOe = sQe + kQBytes;   // dO of the step whose dP is computed next
+    uint8_t* sQl = sDOe + kQBytes;   // Q of the step whose dk is accumulated next: two 64-row halves
+    uint8_t* sDOl = sQl + kQBytes;   // dO of the step whose dv is accumulated next: two 64-row halves
+    uint8_t* sP = sDOl + kQBytes;
     uint8_t* sDS = sP + kBufBytes;
     uint64_t* bars = (uint64_t*)(sDS + kBufBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumKvBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     SchedRing<KvWork>* ring = (SchedRing<KvWork>*)(tmem_slot + 2);
+    float* sc_w = (float*)(tmem_slot + 20);  // [key half][128 rows]: carry_w of the step
+    float* sc_c = sc_w + 256;                // [key half][128 rows]: carry_c of the step
+    float* sc_d = sc_c + 256;                // [128 rows]: drem of the step
+    static_assert(sizeof(SchedRing<KvWork>) <= 72, "ring does not fit its place");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < kNumKvBars; ++i) {
             uint32_t cnt = 1;
-            if (i == B_PDS_READY || i == B_DKV_FREE) cnt = 256;
-            if (i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) cnt = 258;  // MMA warp (one lane), dO producer, 256 row threads
+            if (i == B_LOADED || i == B_DKV_FREE) cnt = 256;
+            if (i == B_PDS_READY0 || i == B_PDS_READY1) cnt = 128;
+            if (i == B_SC_FULL) cnt = 32;
+            if (i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) cnt = 259;  // MMA warp (one lane), two producers, 256 row threads
             mbar_init(&bars[i], cnt);
         }
         *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
@@ -495,6 +572,8 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
         tma_prefetch_desc(&map_do);
+        tma_prefetch_desc(&map_q64);
+        tma_prefetch_desc(&map_do64);
     }
     tc_fence_before();
     __syncthreads();
@@ -502,11 +581,10 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t tmem = *tmem_slot;
     const int n_items = a.hdr->n_items;
     const int n_work = *abort_flag ? 0 : n_items * a.heads;
-    // G counts query-tile steps over all items of this block: step G uses Q stage G & 1; a barrier that completes
-    // once per use is in phase (use count) & 1.
+    // G counts query-tile steps over all items of this block; a barrier that completes once per step is in phase G & 1.
 
     if (warp == 8) {
-        // ------------------------------------------------------------------ TMA: K, V per item, Q ring
+        // ------------------------------------------------------------------ TMA: K, V per item; Q, dO tiles for S, dP
         if (lane == 0) {
             uint32_t G = 0, items = 0;
             bool ok = true;
@@ -525,18 +603,19 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tma_load_4d(sV + bx * kQBox, &map_v, &bars[B_KV_FULL], bx * 64, wk.start + wk.kt * kKT, wk.h, wk.b);
                 }
                 for (int i = wk.kt; i < wk.n_qt; ++i, ++G) {
-                    const uint32_t st = G & 1;
-                    ok = mbar_wait(&bars[B_Q_EMPTY0 + st], ((G >> 1) & 1) ^ 1, abort_flag);
+                    ok = mbar_wait(&bars[B_E_EMPTY], (G & 1) ^ 1, abort_flag);
                     if (!ok) break;
-                    mbar_expect_tx(&bars[B_Q_FULL0 + st], kQBytes);
+                    mbar_expect_tx(&bars[B_E_FULL], 2 * kQBytes);
 #pragma unroll
-                    for (int bx = 0; bx < kBoxes; ++bx)
-                        tma_load_4d(sQ + st * kQBytes + bx * kQBox, &map_q, &bars[B_Q_FULL0 + st], bx * 64, wk.start + i * kBM, wk.h, wk.b);
+                    for (int bx = 0; bx < kBoxes; ++bx) {
+                        tma_load_4d(sQe + bx * kQBox, &map_q, &bars[B_E_FULL], bx * 64, wk.start + i * kBM, wk.h, wk.b);
+                        tma_load_4d(sDOe + bx * kQBox, &map_do, &bars[B_E_FULL], bx * 64, wk.start + i * kBM, wk.h, wk.b);
+                    }
                 }
             }
         }
     } else if (warp == 10) {
-        // ------------------------------------------------------------------ TMA: dO (single stage)
+        // ------------------------------------------------------------------ TMA: 64-row halves of Q, dO for dk, dv
         if (lane == 0) {
             uint32_t G = 0;
             bool ok = true;
@@ -544,14 +623,72 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             int w;
             KvWork wk;
             while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk)) >= 0) {
-                for (int i = wk.kt; i < wk.n_qt; ++i, ++G) {
-                    ok = mbar_wait(&bars[B_DO_EMPTY], (G & 1) ^ 1, abort_flag);
-                    if (!ok) break;
-                    mbar_expect_tx(&bars[B_DO_FULL], kQBytes);
+                for (int i = wk.kt; ok && i < wk.n_qt; ++i, ++G) {
 #pragma unroll
-                    for (int bx = 0; bx < kBoxes; ++bx)
-                        tma_load_4d(sDO + bx * kQBox, &map_do, &bars[B_DO_FULL], bx * 64, wk.start + i * kBM, wk.h, wk.b);
+                    for (int hh = 0; hh < 2; ++hh) {
+                        ok = mbar_wait(&bars[B_L_EMPTY0 + hh], (G & 1) ^ 1, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(&bars[B_L_FULL0 + hh], kQBytes);
+#pragma unroll
+                        for (int bx = 0; bx < kBoxes; ++bx) {
+                            tma_load_4d(sQl + hh * kHalfBytes + bx * kKBox, &map_q64, &bars[B_L_FULL0 + hh], bx * 64,
+                                        wk.start + i * kBM + hh * 64, wk.h, wk.b);
+                            tma_load_4d(sDOl + hh * kHalfBytes + bx * kKBox, &map_do64, &bars[B_L_FULL0 + hh], bx * 64,
+                                        wk.start + i * kBM + hh * 64, wk.h, wk.b);
+                        }
+                    }
                 }
+            }
+        }
+    } else if (warp == 11) {
+        // ------------------------------------------------------------------ per-row scalars of the next step
+        // plain loads by a warp that has nothing else to do: the row threads never wait for global memory
+        uint32_t G = 0;
+        bool ok = true;
+        SchedConsumer sched;
+        int w;
+        KvWork wk;
+        while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk, lane == 0, true)) >= 0) {
+            const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ;
+            const float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ;
+            for (int i = wk.kt; i < wk.n_qt; ++i, ++G) {
+                float vw[2][4], vc[2][4], vd[4];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    const int r = m * 32 + lane, qi = i * kBM + r;
+                    const bool row_ok = qi < wk.len;
+                    vd[m] = 0.f;
+                    if (row_ok) {
+                        const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh +
+                                                            (int64_t)(wk.start + qi) * a.d_rem.st);
+                        vd[m] = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
+                    }
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        const int kh = 2 * wk.kt + hf;
+                        vw[hf][m] = 0.f;
+                        vc[hf][m] = 0.f;
+                        if (row_ok && kh * kBK < wk.len) {  // the half may lie beyond the end of the sequence
+                            const int64_t slot = carry_slot(wk.slot_base, i, kh) * kTileQ + r;
+                            vw[hf][m] = cw[slot];
+                            vc[hf][m] = cc[slot];
+                        }
+                    }
+                }
+                // every row thread has read the scalars of the previous step once it has arrived at B_LOADED
+                if (G > 0) ok = mbar_wait(&bars[B_LOADED], (G - 1) & 1, abort_flag);
+                if (!ok) break;
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    const int r = m * 32 + lane;
+                    sc_d[r] = vd[m];
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        sc_w[hf * 128 + r] = vw[hf][m];
+                        sc_c[hf * 128 + r] = vc[hf][m];
+                    }
+                }
+                mbar_arrive(&bars[B_SC_FULL]);
             }
         }
     } else if (warp == 9) {
@@ -559,143 +696,176 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         {
             const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
             constexpr uint32_t idesc_s = make_idesc(kBM, kKT, kF16 ? 0 : 1, 0, 0);
-            constexpr uint32_t idesc_t = make_idesc(D, kKT, kF16 ? 0 : 1, 1, 1);  // (dO^T or Q^T)[D x q] * (P or dS)[q x 128]
-            const SmemDesc desc_q = make_desc(smem_u32(sQ), 0, 1024), desc_do = make_desc(smem_u32(sDO), 0, 1024);  // K-major
+            constexpr uint32_t idesc_t = make_idesc(kKT, D, kF16 ? 0 : 1, 1, 1);  // (P^T or dS^T)[128 keys x q] * (dO or Q)[q x D]
+            const SmemDesc desc_q = make_desc(smem_u32(sQe), 0, 1024), desc_do = make_desc(smem_u32(sDOe), 0, 1024);  // K-major
             const SmemDesc desc_k = make_desc(smem_u32(sK), 0, 1024), desc_v = make_desc(smem_u32(sV), 0, 1024);
-            const SmemDesc desc_qmn = make_desc(smem_u32(sQ), kQBox, 1024), desc_domn = make_desc(smem_u32(sDO), kQBox, 1024);  // MN-major
-            const SmemDesc desc_p = make_desc(smem_u32(sP), kQBox, 1024), desc_ds = make_desc(smem_u32(sDS), kQBox, 1024);
-            uint32_t G = 0, items = 0;
+            const SmemDesc desc_qmn = make_desc(smem_u32(sQl), kKBox, 1024), desc_domn = make_desc(smem_u32(sDOl), kKBox, 1024);  // MN-major
+            const SmemDesc desc_p = make_desc(smem_u32(sP), kKBox, 1024), desc_ds = make_desc(smem_u32(sDS), kKBox, 1024);
             bool ok = true;
             SB_TRACE_DECL(m);
+            auto issue_sdp = [&](uint32_t g, bool last_of_item) {
+                ok = mbar_wait(&bars[B_E_FULL], g & 1, abort_flag);
+                if (!ok) return;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t o = (k >> 2) * kQBox + (k & 3) * 32;
+                    if (k == 0) mma_ss<false>(leader, tmem + kColS, desc_q, o, desc_k, o, idesc_s);
+                    else mma_ss<true>(leader, tmem + kColS, desc_q, o, desc_k, o, idesc_s);
+                }
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t o = (k >> 2) * kQBox + (k & 3) * 32;
+                    if (k == 0) mma_ss<false>(leader, tmem + kColDP, desc_do, o, desc_v, o, idesc_s);
+                    else mma_ss<true>(leader, tmem + kColDP, desc_do, o, desc_v, o, idesc_s);
+                }
+                mma_commit(leader, &bars[B_SDP_READY]);
+                mma_commit(leader, &bars[B_E_EMPTY]);
+                if (last_of_item) mma_commit(leader, &bars[B_KV_EMPTY]);
+            };
+            // The steps of all items form one stream: S, dP of the first step of the next item are issued while the row
+            // threads still work on the last step of this one (K, V are free after the item's last S, dP).
             SchedConsumer sched;
-            int w;
-            KvWork wk;
-            while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk, leader, true)) >= 0) {
+            KvWork wk, nx;
+            uint32_t g = 0, items = 0;
+            bool have = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk, leader, true) >= 0;
+            if (have) {
+                ok = mbar_wait(&bars[B_KV_FULL], 0, abort_flag);
+                if (ok) issue_sdp(0, wk.n_qt - wk.kt == 1);
+            }
+            while (ok && have) {
                 const int n = wk.n_qt - wk.kt;
-                ok = mbar_wait(&bars[B_KV_FULL], items & 1, abort_flag);
-                for (int j = 0; ok && j < n; ++j) {
-                    const uint32_t g = G + j, st = g & 1;
-                    const SmemDesc dq = {desc_q.lo + st * (kQBytes >> 4), desc_q.hi};
-                    const SmemDesc dqmn = {desc_qmn.lo + st * (kQBytes >> 4), desc_qmn.hi};
+                bool have_next = false;
+                for (int j = 0; ok && j < n; ++j, ++g) {
+                    // S, dP of the following step as soon as this step's are in registers
                     SB_TRACE_EV(m, 0, 1);
-                    ok = mbar_wait(&bars[B_Q_FULL0 + st], (g >> 1) & 1, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int k = 0; k < D / 16; ++k) {
-                        const uint32_t o = (k >> 2) * kQBox + (k & 3) * 32;
-                        if (k == 0) mma_ss<false>(leader, tmem + kColS, dq, o, desc_k, o, idesc_s);
-                        else mma_ss<true>(leader, tmem + kColS, dq, o, desc_k, o, idesc_s);
-                    }
-                    ok = mbar_wait(&bars[B_DO_FULL], g & 1, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int k = 0; k < D / 16; ++k) {
-                        const uint32_t o = (k >> 2) * kQBox + (k & 3) * 32;
-                        if (k == 0) mma_ss<false>(leader, tmem + kColDP, desc_do, o, desc_v, o, idesc_s);
-                        else mma_ss<true>(leader, tmem + kColDP, desc_do, o, desc_v, o, idesc_s);
-                    }
-                    mma_commit(leader, &bars[B_SDP_READY]);
-                    if (j == n - 1) mma_commit(leader, &bars[B_KV_EMPTY]);
-                    SB_TRACE_EV(m, 0, 2);
-                    ok = mbar_wait(&bars[B_PDS_READY], g & 1, abort_flag);
-                    if (!ok) break;
-                    SB_TRACE_EV(m, 0, 3);
-                    if (j == 0) {  // the previous item's accumulators must have been read out
-                        ok = mbar_wait(&bars[B_DKV_FREE], (items & 1) ^ 1, abort_flag);
+                    if (j + 1 < n) {
+                        ok = mbar_wait(&bars[B_LOADED], g & 1, abort_flag);
                         if (!ok) break;
+                        SB_TRACE_EV(m, 0, 2);
+                        tc_fence_after();
+                        issue_sdp(g + 1, j + 2 == n);
+                    } else {
+                        have_next = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, nx, leader, true) >= 0;
+                        if (have_next) {
+                            ok = mbar_wait(&bars[B_LOADED], g & 1, abort_flag) &&
+                                 mbar_wait(&bars[B_KV_FULL], (items + 1) & 1, abort_flag);
+                            if (!ok) break;
+                            SB_TRACE_EV(m, 0, 2);
+                            tc_fence_after();
+                            issue_sdp(g + 1, nx.n_qt - nx.kt == 1);
+                        }
                     }
-                    tc_fence_after();
+                    if (!ok) break;
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        if (kk == 0) mma_ss_dyn(leader, tmem + kColDV, desc_domn, 0, desc_p, 0, idesc_t, j > 0);
-                        else mma_ss<true>(leader, tmem + kColDV, desc_domn, kk * 2048, desc_p, kk * 2048, idesc_t);
-                    }
-                    mma_commit(leader, &bars[B_DO_EMPTY]);
+                    for (int hh = 0; hh < 2; ++hh) {
+                        SB_TRACE_EV(m, 0, 3 + 2 * hh);
+                        ok = mbar_wait(&bars[B_PDS_READY0 + hh], g & 1, abort_flag) &&
+                             mbar_wait(&bars[B_L_FULL0 + hh], g & 1, abort_flag);
+                        if (ok && j == 0 && hh == 0)  // the previous item's accumulators must have been read out
+                            ok = mbar_wait(&bars[B_DKV_FREE], (items & 1) ^ 1, abort_flag);
+                        if (!ok) break;
+                        SB_TRACE_EV(m, 0, 4 + 2 * hh);
+                        tc_fence_after();
+                        const SmemDesc ddo = {desc_domn.lo + hh * (kHalfBytes >> 4), desc_domn.hi};
+                        const SmemDesc dq = {desc_qmn.lo + hh * (kHalfBytes >> 4), desc_qmn.hi};
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        if (kk == 0) mma_ss_dyn(leader, tmem + kColDK, dqmn, 0, desc_ds, 0, idesc_t, j > 0);
-                        else mma_ss<true>(leader, tmem + kColDK, dqmn, kk * 2048, desc_ds, kk * 2048, idesc_t);
+                        for (int kk = 0; kk < 4; ++kk) {
+                            if (kk == 0) mma_ss_dyn(leader, tmem + kColDV, desc_p, 0, ddo, 0, idesc_t, j > 0 || hh > 0);
+                            else mma_ss<true>(leader, tmem + kColDV, desc_p, kk * 2048, ddo, kk * 2048, idesc_t);
+                        }
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            if (kk == 0) mma_ss_dyn(leader, tmem + kColDK, desc_ds, 0, dq, 0, idesc_t, j > 0 || hh > 0);
+                            else mma_ss<true>(leader, tmem + kColDK, desc_ds, kk * 2048, dq, kk * 2048, idesc_t);
+                        }
+                        mma_commit(leader, &bars[B_PDS_FREE0 + hh]);
+                        mma_commit(leader, &bars[B_L_EMPTY0 + hh]);
                     }
-                    mma_commit(leader, &bars[B_Q_EMPTY0 + st]);
-                    SB_TRACE_EV(m, 0, 4);
                 }
                 if (!ok) break;
                 mma_commit(leader, &bars[B_DKV_READY]);
-                G += n;
                 ++items;
+                wk = nx;
+                have = have_next;
             }
         }
     } else {
-        // ------------------------------------------------------------------ row threads: group 0 right half, group 1 left half
+        // ------------------------------------------------------------------ row threads
         const int grp = warp >> 2;
-        const int hf = grp ^ 1;  // 64-key half of the tile this thread owns
+        const int hf = grp ^ 1;          // 64-key half of the tile this thread owns
+        const int hh = (warp & 3) >> 1;  // half of the query rows this thread belongs to
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const float scale = a.inv_temp * kLog2e;
-        uint8_t* prow = sP + hf * kQBox + r * 128;
-        uint8_t* srow = sDS + hf * kQBox + r * 128;
+        uint8_t* prow = sP + hf * kKBox + (r & 63) * 128;
+        uint8_t* srow = sDS + hf * kKBox + (r & 63) * 128;
         uint32_t G = 0, items = 0;
         bool ok = true;
         SB_TRACE_DECL(c);
+        // dk (group 0) / dv (group 1) of a finished item are stored in the first step of the next item (after its
+        // arithmetic, before its p / ds go to shared memory), so that nobody idles while the last contractions drain
+        auto store_dkdv = [&](const KvWork& e, uint32_t item) {
+            ok = mbar_wait(&bars[B_DKV_READY], item & 1, abort_flag);
+            if (!ok) return;
+            if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 6);
+            kv_store_rows<D, kF16>(grp == 0 ? a.dk : a.dv, grp == 0 ? a.inv_temp : 1.f, e, r,
+                                   lane_base + (grp == 0 ? kColDK : kColDV));
+            mbar_arrive(&bars[B_DKV_FREE]);
+            if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 7);
+        };
         SchedConsumer sched;
         int w;
-        KvWork wk;
+        KvWork wk, done;
+        bool pending = false;
         while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk)) >= 0) {
             const int n = wk.n_qt - wk.kt;
             const int kh = 2 * wk.kt + hf;
-            const bool half_ok = kh * kBK < wk.len;  // the half may lie beyond the end of the sequence
-            const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
-            const float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
-            // per-row scalars of a step (carry of W, prefix of g, drem): loaded one step ahead
-            float nW = 0.f, nC = 0.f, nD = 0.f;
-            auto load_scalars = [&](int i) {
-                const int qi = i * kBM + r;
-                nW = 0.f; nC = 0.f; nD = 0.f;
-                if (half_ok && i < wk.n_qt && qi < wk.len) {
-                    const int64_t slot = carry_slot(wk.slot_base, i, kh) * kTileQ;
-                    nW = cw[slot];
-                    nC = cc[slot];
-                    const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh +
-                                                        (int64_t)(wk.start + qi) * a.d_rem.st);
-                    nD = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
-                }
-            };
-            load_scalars(wk.kt);
             for (int j = 0; j < n; ++j) {
                 const int i = wk.kt + j;
                 const uint32_t g = G + j;
                 const int qi = i * kBM + r;
-                float W = nW;
-                const float cright = nC, drem = nD;
-                load_scalars(i + 1);
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 1);
+                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 1);
+                ok = mbar_wait(&bars[B_SC_FULL], g & 1, abort_flag);
+                if (!ok) break;
+                float W = sc_w[hf * 128 + r];
+                float c = sc_c[hf * 128 + r];  // prefix of g through the right edge of this half; loses every g it passes
+                const float drem = sc_d[r];
                 ok = mbar_wait(&bars[B_SDP_READY], g & 1, abort_flag);
                 if (!ok) break;
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 2);
+                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 2);
                 tc_fence_after();
                 const bool masked = i == wk.kt;
                 const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
                 uint32_t pp[32], ps[32];
-                float c = cright;  // prefix of g through the right edge of this half; loses every g it passes
                 {
-                    uint32_t s[32], dp[32];
-                    tmem_ld32(lane_base + kColS + 64 * hf + 32, s);
-                    tmem_ld32(lane_base + kColDP + 64 * hf + 32, dp);
+                    uint32_t s1[32], d1[32], s0[32], d0[32];
+                    tmem_ld32(lane_base + kColS + 64 * hf + 32, s1);
+                    tmem_ld32(lane_base + kColDP + 64 * hf + 32, d1);
+                    tmem_ld32(lane_base + kColS + 64 * hf, s0);
+                    tmem_ld32(lane_base + kColDP + 64 * hf, d0);
                     tmem_wait_ld();
-                    if (masked) kv_chunk<true, kF16>(s, dp, scale, 32, lim, drem, c, W, pp + 16, ps + 16);
-                    else kv_chunk<false, kF16>(s, dp, scale, 32, lim, drem, c, W, pp + 16, ps + 16);
-                    tmem_ld32(lane_base + kColS + 64 * hf, s);
-                    tmem_ld32(lane_base + kColDP + 64 * hf, dp);
-                    tmem_wait_ld();
-                    if (masked) kv_chunk<true, kF16>(s, dp, scale, 0, lim, drem, c, W, pp, ps);
-                    else kv_chunk<false, kF16>(s, dp, scale, 0, lim, drem, c, W, pp, ps);
+                    tc_fence_before();
+                    mbar_arrive(&bars[B_LOADED]);  // S, dP and the scalars of this step are free
+                    if (masked) {
+                        kv_chunk<true, kF16>(s1, d1, scale, 32, lim, drem, c, W, pp + 16, ps + 16);
+                        kv_chunk<true, kF16>(s0, d0, scale, 0, lim, drem, c, W, pp, ps);
+                    } else {
+                        kv_chunk<false, kF16>(s1, d1, scale, 32, lim, drem, c, W, pp + 16, ps + 16);
+                        kv_chunk<false, kF16>(s0, d0, scale, 0, lim, drem, c, W, pp, ps);
+                    }
                 }
-                tc_fence_before();
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 3);
-                // S / dP of this step became ready only after dv^T, dk^T of the previous one had completed (they were
-                // issued earlier by the same thread), so the p / ds tiles in shared memory are free to overwrite
+                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 3);
+                if (j == 0 && pending) {
+                    store_dkdv(done, items - 1);
+                    if (!ok) break;
+                }
+                // the p / ds buffers are free once the contractions of their previous use are complete: the other half's,
+                // of the previous step for half 0 and of this step for half 1 (one barrier per half, so that a waiter
+                // is never two phases away from the phase it names)
+                ok = mbar_wait(&bars[B_PDS_FREE0 + (hh ^ 1)], (g & 1) ^ (hh ^ 1), abort_flag);
+                if (!ok) break;
+                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 4);
 #pragma unroll
                 for (int ch = 0; ch < 8; ++ch) {
                     const int off = (ch ^ (r & 7)) << 4;
@@ -703,46 +873,16 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     *(uint4*)(srow + off) = make_uint4(ps[4 * ch], ps[4 * ch + 1], ps[4 * ch + 2], ps[4 * ch + 3]);
                 }
                 fence_async_smem();
-                mbar_arrive(&bars[B_PDS_READY]);
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 4);
+                mbar_arrive(&bars[B_PDS_READY0 + hh]);
+                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 5);
             }
             if (!ok) break;
-            // epilogue: group 0 stores dk, group 1 dv; a thread holds one head-dim index d, the 128 keys along the columns
-            ok = mbar_wait(&bars[B_DKV_READY], items & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            const int d = D == 128 ? r : ((warp & 3) * 16 + lane);
-            const bool d_ok = D == 128 ? true : lane < 16;
-            const int keys_valid = min(kKT, wk.len - wk.kt * kKT);
-            {
-                const MatView& m = grp == 0 ? a.dk : a.dv;
-                const float sc = grp == 0 ? a.inv_temp : 1.f;
-                char* base = m.ptr + 2 * ((int64_t)wk.b * m.sb + (int64_t)wk.h * m.sh +
-                                          (int64_t)(wk.start + wk.kt * kKT) * m.st + d);
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint32_t v[32];
-                    tmem_ld32(lane_base + (grp == 0 ? kColDK : kColDV) + q4 * 32, v);
-                    tmem_wait_ld();
-                    if (d_ok) {
-#pragma unroll
-                        for (int jj = 0; jj < 32; ++jj) {
-                            const int key = q4 * 32 + jj;
-                            if (key < keys_valid) {
-                                const float x = __uint_as_float(v[jj]) * sc;
-                                char* ptr = base + 2 * (int64_t)key * m.st;
-                                if (kF16) *(__half*)ptr = __float2half_rn(x);
-                                else *(__nv_bfloat16*)ptr = __float2bfloat16_rn(x);
-                            }
-                        }
-                    }
-                }
-            }
-            tc_fence_before();
-            mbar_arrive(&bars[B_DKV_FREE]);
+            done = wk;
+            pending = true;
             G += n;
             ++items;
         }
+        if (ok && pending) store_dkdv(done, items - 1);
     }
     tc_teardown(abort_flag, a.status, tmem, kCols, 9);
     sched_finish(a.sched + 4);
@@ -758,14 +898,15 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         encode_tile_map(&mk, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBK) ||
         encode_tile_map(&mv, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBK))
         return 1;
-    CUtensorMap mk128, mv128;  // the dk/dv kernel loads K and V as 128-row tiles
+    CUtensorMap mk128, mv128, mq64, mdo64;  // the dk/dv kernel loads K and V as 128-row tiles, Q and dO also as 64-row halves
     if (encode_tile_map(&mk128, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBM) ||
-        encode_tile_map(&mv128, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBM))
+        encode_tile_map(&mv128, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBM) ||
+        encode_tile_map(&mq64, p.q.ptr, kind, D, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBK) ||
+        encode_tile_map(&mdo64, p.d_o.ptr, kind, D, p.tokens, p.heads, B, p.d_o.stride_t, p.d_o.stride_h, p.d_o.stride_b, kBK))
         return 1;
-    // dq kernel: 2 x (128 x D) + 3 x (64 x D) 16-bit tiles (q, do, 2 k stages, v); dk/dv kernel: k, v, 2 q stages, do, p, ds
+    // dq kernel: q, do, four k stages, three v stages; dk/dv kernel: k, v, early q / do, late q / do, p, ds, scalars
     constexpr int need = 2 * kBM * D * 2 + (kDqKStages + kDqVStages) * kBK * D * 2 + 4096;
-    constexpr int need_b = 5 * kBM * D * 2 + 2 * 2 * 128 * 128 + 512;
-    // at least 80 KB so that never more than two blocks (2 x 256 tensor-memory columns) share an SM
+    constexpr int need_b = 6 * kBM * D * 2 + 2 * 2 * 64 * 128 + 3072;
     constexpr int smem_a = need > 120 * 1024 ? need : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
     constexpr int smem_b = need_b > 120 * 1024 ? need_b : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
     cudaError_t e = cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
@@ -774,11 +915,10 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    const int grid = 2 * sm_count();
     if (p.bwd_phases != SBATTN_BWD_DKDV) tc_bwd_dq_kernel<D, kF16><<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk, mv, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, a);
+    if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, mq64, mdo64, a);
     return (int)cudaGetLastError();
 }
 
