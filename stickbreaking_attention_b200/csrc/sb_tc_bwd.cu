@@ -58,21 +58,23 @@ __device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, f
 }
 
 // ================================================================================================ dq kernel
-// One block per SM (352 threads), one work item = (head, sequence, 128-row query tile) at a time.  Warps 0-3 / 4-7 are
-// two row groups that take the 64-key tiles of the item in turn, left to right; S and dP live in three buffer pairs in
-// tensor memory, so while the groups work on tiles j and j+1 the tensor cores run dQ += dS K of tile j-1 and S, dP of
-// tile j+2 (with two pairs the next S, dP would have to wait for the dQ contraction that reads dS out of the same columns).
-// The weights of a tile are entered with the forward's carry (carry_w); the prefix of g that ds needs travels from
-// group to group through shared memory: a thread first computes a = g - beta * (prefix inside the tile), then receives
-// the prefix at the tile's left edge from its partner thread in the other group, passes its own on, and finishes
-// ds = a - beta * prefix.  Warp 8 loads Q, dO (once per item) and the K tiles (four-stage ring: a K tile is needed for S
-// early and for dQ late), warp 10 the V tiles, warp 9 issues every tcgen05.mma.
+// One block per SM (352 threads), one work item = (head, sequence, 128-row query tile) at a time, walked LEFT TO RIGHT in
+// steps of 128 keys, so that every contraction runs at the widest shape: S and dP [128 q x 128 keys], dQ += dS K with
+// K = 128 (an MMA instruction costs the same for N = 64 and N = 128; 64-key steps need 40 instructions per 128 x 128
+// scores, 128-key steps 24).  Warps 0-3 own the right 64 keys of a step, warps 4-7 the left 64 keys, one thread per
+// query row in each; the halves are entered independently with the forward's carry (carry_w exists at every 64-key
+// boundary).  The prefix of g that ds needs is local to a half up to a constant: a thread computes
+// a = g - beta * (prefix inside its half), the two threads of a row exchange the totals of their halves through shared
+// memory, and ds = a - beta * (prefix at the half's left edge).
+// Tensor memory: S in two buffers (S of the next step is computed while this one is worked on; dS overwrites the left
+// half of its S buffer as 16-bit operands), dP in one (released as soon as every thread has copied its values to
+// registers), dQ.  Warp 8 loads Q, dO (once per item) and the K tiles (three-stage ring: a K tile is needed for S early
+// and for dQ late), warp 10 the V tiles, warp 9 issues every tcgen05.mma.
 constexpr int kDqThreads = 352;
-constexpr int kDqKStages = 4, kDqVStages = 3;
-enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_FULL2, A_K_FULL3, A_K_EMPTY0, A_K_EMPTY1, A_K_EMPTY2, A_K_EMPTY3,
-             A_V_FULL0, A_V_FULL1, A_V_FULL2, A_V_EMPTY0, A_V_EMPTY1, A_V_EMPTY2, A_SDP_READY0, A_SDP_READY1, A_SDP_READY2,
-             A_DS_READY0, A_DS_READY1, A_DS_READY2, A_X_C0, A_X_C1, A_DQ_READY, A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1,
-             kNumDqBars };
+constexpr int kDqKStages = 3, kDqVStages = 2;
+enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_FULL2, A_K_EMPTY0, A_K_EMPTY1, A_K_EMPTY2, A_V_FULL0, A_V_FULL1,
+             A_V_EMPTY0, A_V_EMPTY1, A_S_READY0, A_S_READY1, A_DP_READY, A_LOADED, A_DS_READY, A_X_G0, A_X_G1, A_X_G2, A_X_G3, A_DQ_READY,
+             A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1, kNumDqBars };
 
 template <bool kMasked>
 __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[32], float scale, int col0, int lim,
@@ -100,7 +102,7 @@ __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[
         }
     }
 }
-// left to right: g <- a = g - beta * (inclusive prefix of g inside the tile); c carries the running prefix
+// left to right: g <- a = g - beta * (inclusive prefix of g inside the half); c carries the running prefix
 __device__ __forceinline__ void dq_half_local(const uint32_t (&beta)[32], uint32_t (&g)[32], float& c) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -108,7 +110,7 @@ __device__ __forceinline__ void dq_half_local(const uint32_t (&beta)[32], uint32
         g[j] = __float_as_uint(fmaf(-__uint_as_float(beta[j]), c, __uint_as_float(g[j])));
     }
 }
-// ds = a - beta * (prefix at the tile's left edge), packed to 16 bits
+// ds = a - beta * (prefix at the half's left edge), packed to 16 bits
 template <bool kF16>
 __device__ __forceinline__ void dq_half_finish(const uint32_t (&beta)[32], const uint32_t (&av)[32], float c_in, uint32_t (&packed)[16]) {
 #pragma unroll
@@ -125,27 +127,29 @@ __global__ void __launch_bounds__(kDqThreads, 1)
 tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const KArgs a) {
     constexpr int kBoxes = D / 64;
-    constexpr int kQBytes = kBM * D * 2, kKBytes = kBK * D * 2;
-    constexpr uint32_t kColS = 0, kColDP = 64, kColDQ = 384;  // S / dP buffer b (of three) at +128*b; dS overwrites the left half of S
+    constexpr int kQBytes = kBM * D * 2;  // a 128-row tile of Q, dO, K or V
+    constexpr int kStep = 128;            // keys per step
+    constexpr uint32_t kColS = 0, kColDP = 256, kColDQ = 384;  // S buffer b at +128*b; dS overwrites columns [0, 64) of its S buffer
     constexpr uint32_t kCols = 512;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sDO = sQ + kQBytes;
     uint8_t* sK = sDO + kQBytes;              // kDqKStages tiles
-    uint8_t* sV = sK + kDqKStages * kKBytes;  // kDqVStages tiles
-    uint64_t* bars = (uint64_t*)(sV + kDqVStages * kKBytes);
+    uint8_t* sV = sK + kDqKStages * kQBytes;  // kDqVStages tiles
+    uint64_t* bars = (uint64_t*)(sV + kDqVStages * kQBytes);
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumDqBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     SchedRing<Work>* ring = (SchedRing<Work>*)(tmem_slot + 2);
-    float* xc = (float*)(tmem_slot + 32);  // [group][128 rows]: prefix of g through the tile the group has just finished
-    float* wpre = xc + 256;               // [parity][group][128 rows]: carry_w of a group's next tile, copied asynchronously
+    float* xg = (float*)(tmem_slot + 32);  // [group][128 rows]: total of g over the group's half of the step
+    float* wpre = xg + 256;                // [group][128 rows]: carry_w of a group's next step, copied asynchronously
+    static_assert(sizeof(SchedRing<Work>) <= 120, "ring does not fit its place");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < kNumDqBars; ++i) {
             uint32_t cnt = 1;
-            if (i == A_DS_READY0 || i == A_DS_READY1 || i == A_DS_READY2 || i == A_X_C0 || i == A_X_C1) cnt = 128;
-            if (i == A_DQ_FREE) cnt = 256;
+            if (i >= A_X_G0 && i <= A_X_G3) cnt = 128;
+            if (i == A_LOADED || i == A_DS_READY || i == A_DQ_FREE) cnt = 256;
             if (i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) cnt = 258;  // MMA warp (one lane), V producer, 256 row threads
             mbar_init(&bars[i], cnt);
         }
@@ -168,8 +172,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t tmem = *tmem_slot;
     const int n_items = a.hdr->n_items;
     const int n_work = *abort_flag ? 0 : n_items * a.heads;
-    // G counts key-tile steps over all items of this block: step G uses K stage G % 4, V stage G % 3 and S/dP buffer
-    // G % 3; a barrier that completes once per use is in phase (use count) & 1.
+    // G counts 128-key steps over all items of this block: step G uses K stage G % 3, V stage G % 2 and S buffer G % 2;
+    // a barrier that completes once per use is in phase (use count) & 1.
 
     if (warp == 8) {
         // ------------------------------------------------------------------ TMA: Q, dO per item, K ring
@@ -181,7 +185,6 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             Work wk;
             const auto fetch = [&](int w_) { return fetch_work(a, n_items, w_); };
             while (ok && (w = sched.next(a.sched + 2, n_work, ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, fetch, wk)) >= 0) {
-                const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
                 ok = mbar_wait(&bars[A_QDO_EMPTY], (items & 1) ^ 1, abort_flag);
                 ++items;
                 if (!ok) break;
@@ -191,14 +194,14 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     tma_load_4d(sQ + bx * kQBox, &map_q, &bars[A_QDO_FULL], bx * 64, wk.start + wk.qt * kBM, wk.h, wk.b);
                     tma_load_4d(sDO + bx * kQBox, &map_do, &bars[A_QDO_FULL], bx * 64, wk.start + wk.qt * kBM, wk.h, wk.b);
                 }
-                for (int kh = 0; kh < n_kh; ++kh, ++G) {
+                for (int j = 0; j <= wk.qt; ++j, ++G) {
                     const uint32_t st = G % kDqKStages;
                     ok = mbar_wait(&bars[A_K_EMPTY0 + st], ((G / kDqKStages) & 1) ^ 1, abort_flag);
                     if (!ok) break;
-                    mbar_expect_tx(&bars[A_K_FULL0 + st], kKBytes);
+                    mbar_expect_tx(&bars[A_K_FULL0 + st], kQBytes);
 #pragma unroll
                     for (int bx = 0; bx < kBoxes; ++bx)
-                        tma_load_4d(sK + st * kKBytes + bx * kKBox, &map_k, &bars[A_K_FULL0 + st], bx * 64, wk.start + kh * kBK, wk.h, wk.b);
+                        tma_load_4d(sK + st * kQBytes + bx * kQBox, &map_k, &bars[A_K_FULL0 + st], bx * 64, wk.start + j * kStep, wk.h, wk.b);
                 }
             }
         }
@@ -211,15 +214,14 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             int w;
             Work wk;
             while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, wk)) >= 0) {
-                const int n_kh = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
-                for (int kh = 0; kh < n_kh; ++kh, ++G) {
-                    const uint32_t st = G % kDqVStages;
-                    ok = mbar_wait(&bars[A_V_EMPTY0 + st], ((G / kDqVStages) & 1) ^ 1, abort_flag);
+                for (int j = 0; j <= wk.qt; ++j, ++G) {
+                    const uint32_t st = G & 1;
+                    ok = mbar_wait(&bars[A_V_EMPTY0 + st], ((G >> 1) & 1) ^ 1, abort_flag);
                     if (!ok) break;
-                    mbar_expect_tx(&bars[A_V_FULL0 + st], kKBytes);
+                    mbar_expect_tx(&bars[A_V_FULL0 + st], kQBytes);
 #pragma unroll
                     for (int bx = 0; bx < kBoxes; ++bx)
-                        tma_load_4d(sV + st * kKBytes + bx * kKBox, &map_v, &bars[A_V_FULL0 + st], bx * 64, wk.start + kh * kBK, wk.h, wk.b);
+                        tma_load_4d(sV + st * kQBytes + bx * kQBox, &map_v, &bars[A_V_FULL0 + st], bx * 64, wk.start + j * kStep, wk.h, wk.b);
                 }
             }
         }
@@ -227,69 +229,79 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         // ------------------------------------------------------------------ MMA issuer
         {
             const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
-            constexpr uint32_t idesc_s = make_idesc(kBM, kBK, kF16 ? 0 : 1, 0, 0);
+            constexpr uint32_t idesc_s = make_idesc(kBM, kStep, kF16 ? 0 : 1, 0, 0);
             constexpr uint32_t idesc_dq = make_idesc(kBM, D, kF16 ? 0 : 1, 0, 1);
             const SmemDesc desc_q = make_desc(smem_u32(sQ), 0, 1024), desc_do = make_desc(smem_u32(sDO), 0, 1024);
             const SmemDesc desc_k = make_desc(smem_u32(sK), 0, 1024), desc_v = make_desc(smem_u32(sV), 0, 1024);
-            const SmemDesc desc_kmn = make_desc(smem_u32(sK), kKBox, 1024);  // K tile as MN-major operand of dQ
+            const SmemDesc desc_kmn = make_desc(smem_u32(sK), kQBox, 1024);  // K tile as MN-major operand of dQ
             uint32_t G = 0, items = 0;
             bool ok = true;
             SB_TRACE_DECL(m);
-            auto issue_sdp = [&](uint32_t g, bool last_of_item) {
-                const uint32_t kst = g % kDqKStages, vst = g % kDqVStages, buf = g % 3;
-                const SmemDesc dk = {desc_k.lo + kst * (kKBytes >> 4), desc_k.hi};
-                const SmemDesc dv = {desc_v.lo + vst * (kKBytes >> 4), desc_v.hi};
+            auto issue_s = [&](uint32_t g) {
+                const uint32_t kst = g % kDqKStages;
+                const SmemDesc dk = {desc_k.lo + kst * (kQBytes >> 4), desc_k.hi};
                 ok = mbar_wait(&bars[A_K_FULL0 + kst], (g / kDqKStages) & 1, abort_flag);
                 if (!ok) return;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
-                    const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                    if (k == 0) mma_ss<false>(leader, tmem + kColS + 128 * buf, desc_q, oq, dk, okk, idesc_s);
-                    else mma_ss<true>(leader, tmem + kColS + 128 * buf, desc_q, oq, dk, okk, idesc_s);
+                    const uint32_t o = (k >> 2) * kQBox + (k & 3) * 32;
+                    if (k == 0) mma_ss<false>(leader, tmem + kColS + 128 * (g & 1), desc_q, o, dk, o, idesc_s);
+                    else mma_ss<true>(leader, tmem + kColS + 128 * (g & 1), desc_q, o, dk, o, idesc_s);
                 }
-                ok = mbar_wait(&bars[A_V_FULL0 + vst], (g / kDqVStages) & 1, abort_flag);
+                mma_commit(leader, &bars[A_S_READY0 + (g & 1)]);
+            };
+            auto issue_dp = [&](uint32_t g, bool last_of_item) {
+                const uint32_t vst = g & 1;
+                const SmemDesc dv = {desc_v.lo + vst * (kQBytes >> 4), desc_v.hi};
+                ok = mbar_wait(&bars[A_V_FULL0 + vst], (g >> 1) & 1, abort_flag);
                 if (!ok) return;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
-                    const uint32_t oq = (k >> 2) * kQBox + (k & 3) * 32, okk = (k >> 2) * kKBox + (k & 3) * 32;
-                    if (k == 0) mma_ss<false>(leader, tmem + kColDP + 128 * buf, desc_do, oq, dv, okk, idesc_s);
-                    else mma_ss<true>(leader, tmem + kColDP + 128 * buf, desc_do, oq, dv, okk, idesc_s);
+                    const uint32_t o = (k >> 2) * kQBox + (k & 3) * 32;
+                    if (k == 0) mma_ss<false>(leader, tmem + kColDP, desc_do, o, dv, o, idesc_s);
+                    else mma_ss<true>(leader, tmem + kColDP, desc_do, o, dv, o, idesc_s);
                 }
-                mma_commit(leader, &bars[A_SDP_READY0 + buf]);
+                mma_commit(leader, &bars[A_DP_READY]);
                 mma_commit(leader, &bars[A_V_EMPTY0 + vst]);
-                if (last_of_item) mma_commit(leader, &bars[A_QDO_EMPTY]);
+                if (last_of_item) mma_commit(leader, &bars[A_QDO_EMPTY]);  // the item's last S was issued before
             };
             SchedConsumer sched;
             int w;
             Work wk;
             while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, wk, leader, true)) >= 0) {
-                const int n = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
+                const int n = wk.qt + 1;
                 ok = mbar_wait(&bars[A_QDO_FULL], items & 1, abort_flag);
                 if (!ok) break;
-                for (int j = 0; ok && j < min(n, 3); ++j) issue_sdp(G + j, j + 1 == n);
+                issue_s(G);
+                if (ok && n > 1) issue_s(G + 1);
+                if (ok) issue_dp(G, n == 1);
                 for (int j = 0; ok && j < n; ++j) {
-                    const uint32_t g = G + j, buf = g % 3, kst = g % kDqKStages;
-                    SB_TRACE_EV(m, 0, 1);
-                    ok = mbar_wait(&bars[A_DS_READY0 + buf], (g / 3) & 1, abort_flag);
-                    if (!ok) break;
-                    SB_TRACE_EV(m, 0, 2);
-                    if (j == 0) {  // the previous item's dQ must have been read out
-                        ok = mbar_wait(&bars[A_DQ_FREE], (items & 1) ^ 1, abort_flag);
+                    const uint32_t g = G + j, kst = g % kDqKStages;
+                    if (j + 1 < n) {  // dP of the next step as soon as this step's is in registers
+                        SB_TRACE_EV(m, 0, 1);
+                        ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_dp(g + 1, j + 2 == n);
                         if (!ok) break;
                     }
+                    SB_TRACE_EV(m, 0, 2);
+                    ok = mbar_wait(&bars[A_DS_READY], g & 1, abort_flag);
+                    if (ok && j == 0) ok = mbar_wait(&bars[A_DQ_FREE], (items & 1) ^ 1, abort_flag);  // previous dQ read out
+                    if (!ok) break;
+                    SB_TRACE_EV(m, 0, 3);
                     tc_fence_after();
-                    const SmemDesc dkmn = {desc_kmn.lo + kst * (kKBytes >> 4), desc_kmn.hi};
-                    const uint32_t a_ds = tmem + kColS + 128 * buf;
+                    const SmemDesc dkmn = {desc_kmn.lo + kst * (kQBytes >> 4), desc_kmn.hi};
+                    const uint32_t a_ds = tmem + kColS + 128 * (g & 1);
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {
+                    for (int k = 0; k < kStep / 16; ++k) {
                         if (k == 0) mma_ts_dyn(leader, tmem + kColDQ, a_ds, dkmn, 0, idesc_dq, j > 0);
                         else mma_ts<true>(leader, tmem + kColDQ, a_ds + k * 8, dkmn, k * 2048, idesc_dq);
                     }
                     mma_commit(leader, &bars[A_K_EMPTY0 + kst]);
-                    SB_TRACE_EV(m, 0, 3);
-                    if (j + 3 < n) issue_sdp(g + 3, j + 4 == n);
+                    if (j + 2 < n) issue_s(g + 2);  // into the buffer whose dS the contraction above reads: in order
                     SB_TRACE_EV(m, 0, 4);
                 }
                 if (!ok) break;
@@ -299,21 +311,20 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
         }
     } else {
-        // ------------------------------------------------------------------ row groups
+        // ------------------------------------------------------------------ row threads: group 0 right half, group 1 left half
         const int grp = warp >> 2;
+        const int hf = grp ^ 1;  // 64-key half of the step this thread owns
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const float scale = a.inv_temp * kLog2e;
-        float* x_mine = xc + grp * 128;
-        const float* x_other = xc + (grp ^ 1) * 128;
-        uint32_t G = 0, items = 0, ph_x = 0;
+        uint32_t G = 0, items = 0;
         bool ok = true;
         SB_TRACE_DECL(c);
         SchedConsumer sched;
         int w;
         Work wk;
         while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, wk)) >= 0) {
-            const int n = min(2 * wk.qt + 2, (wk.len + kBK - 1) / kBK);
+            const int n = wk.qt + 1;
             const int qi = wk.qt * kBM + r;
             const bool row_ok = qi < wk.len;
             const int64_t tok = wk.start + qi;
@@ -324,29 +335,36 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
-            // the carry of a tile is copied to shared memory one tile ahead (cp.async): held in a register it would be
+            // the carry of a step is copied to shared memory one step ahead (cp.async): held in a register it would be
             // spilled, and the spill store would wait for the load
             float* wslot = wpre + grp * 128 + r;
-            if (row_ok && grp < n) cp_async4(wslot, cw + carry_slot(wk.slot_base, wk.qt, grp) * kTileQ);
-            for (int j = grp, it = 0; j < n; j += 2, it ^= 1) {
-                const uint32_t g = G + j, buf = g % 3;
-                const int64_t slot = carry_slot(wk.slot_base, wk.qt, j) * kTileQ;
+            // the half may lie beyond the end of the sequence (its carry slot does not exist): then W = 0, no weights
+            const auto half_ok = [&](int j) { return row_ok && (2 * j + hf) * kBK < wk.len; };
+            if (half_ok(0)) cp_async4(wslot, cw + carry_slot(wk.slot_base, wk.qt, hf) * kTileQ);
+            float c_in = 0.f;  // prefix of g at the left edge of the step
+            for (int j = 0; j < n; ++j) {
+                const uint32_t g = G + j, buf = g & 1;
+                const int kh = 2 * j + hf;
+                const int64_t slot = carry_slot(wk.slot_base, wk.qt, kh) * kTileQ;
                 cp_async_wait_all();
-                float W = row_ok ? wslot[it * 256] : 0.f;
-                if (row_ok && j + 2 < n) cp_async4(wslot + (it ^ 1) * 256, cw + slot + 2 * kTileQ);
+                float W = half_ok(j) ? *wslot : 0.f;
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 1);
-                ok = mbar_wait(&bars[A_SDP_READY0 + buf], (g / 3) & 1, abort_flag);
+                ok = mbar_wait(&bars[A_S_READY0 + buf], (g >> 1) & 1, abort_flag) && mbar_wait(&bars[A_DP_READY], g & 1, abort_flag);
                 if (!ok) break;
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 2);
                 tc_fence_after();
-                const bool masked = j >= 2 * wk.qt;  // the tile reaches the diagonal
-                const int lim = min(kBK, max(0, qi - j * kBK + a.attend_current));
+                const bool masked = kh >= 2 * wk.qt;  // the half reaches the diagonal
+                const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
                 uint32_t sr[32], gr[32], sl[32], gl[32], packed[16];
-                tmem_ld32(lane_base + kColS + 128 * buf + 32, sr);
-                tmem_ld32(lane_base + kColDP + 128 * buf + 32, gr);
-                tmem_ld32(lane_base + kColS + 128 * buf, sl);
-                tmem_ld32(lane_base + kColDP + 128 * buf, gl);
+                tmem_ld32(lane_base + kColS + 128 * buf + 64 * hf + 32, sr);
+                tmem_ld32(lane_base + kColDP + 64 * hf + 32, gr);
+                tmem_ld32(lane_base + kColS + 128 * buf + 64 * hf, sl);
+                tmem_ld32(lane_base + kColDP + 64 * hf, gl);
                 tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(&bars[A_LOADED]);  // dP is free; so are the S columns that dS will overwrite, once all have arrived
+                // next step's carry into the slot read above (the read is long complete: W has been used)
+                if (j + 1 < n && half_ok(j + 1)) cp_async4(wslot, cw + slot + 2 * kTileQ);
                 if (masked) {
                     dq_half_pass1<true>(sr, gr, scale, 32, lim, drem, W);
                     dq_half_pass1<true>(sl, gl, scale, 0, lim, drem, W);
@@ -354,32 +372,32 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     dq_half_pass1<false>(sr, gr, scale, 32, lim, drem, W);
                     dq_half_pass1<false>(sl, gl, scale, 0, lim, drem, W);
                 }
-                float cl = 0.f;  // prefix of g inside the tile
+                float cl = 0.f;  // prefix of g inside the half
                 dq_half_local(sl, gl, cl);
                 dq_half_local(sr, gr, cl);
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 3);
-                // prefix at the tile's left edge: from the partner thread, which handled the tile to the left
-                float c_in = 0.f;
-                if (j > 0) {
-                    ok = mbar_wait(&bars[A_X_C0 + (grp ^ 1)], ph_x, abort_flag);
-                    ph_x ^= 1;
-                    if (!ok) break;
-                    c_in = x_other[r];
-                }
-                const float c_out = c_in + cl;
-                if (j + 1 < n) {
-                    x_mine[r] = c_out;
-                    mbar_arrive(&bars[A_X_C0 + grp]);
-                }
-                if (row_ok) cc[slot] = c_out;  // prefix through the right edge of this tile, for the dk/dv kernel
+                // The two threads of a row exchange the totals of their halves.  Every thread has begun this step (and so
+                // has read the previous step's total) once it has arrived at A_LOADED; two barriers per group, by step
+                // parity, so that a waiter is never two phases away from the phase it names.
+                ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
+                if (!ok) break;
+                xg[grp * 128 + r] = cl;
+                mbar_arrive(&bars[A_X_G0 + 2 * grp + (g & 1)]);
+                ok = mbar_wait(&bars[A_X_G0 + 2 * (grp ^ 1) + (g & 1)], (g >> 1) & 1, abort_flag);
+                if (!ok) break;
+                const float other = xg[(grp ^ 1) * 128 + r];
+                const float c_edge = hf ? c_in + other : c_in;  // prefix at the left edge of this half
+                if (half_ok(j)) cc[slot] = c_edge + cl;         // prefix through its right edge, for the dk/dv kernel
+                c_in += cl + other;
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 4);
-                dq_half_finish<kF16>(sl, gl, c_in, packed);
-                tmem_st16(lane_base + kColS + 128 * buf, packed);
-                dq_half_finish<kF16>(sr, gr, c_in, packed);
-                tmem_st16(lane_base + kColS + 128 * buf + 16, packed);
+                // dS goes to columns [0, 64) of the S buffer: every thread has read its scores (A_LOADED, above)
+                dq_half_finish<kF16>(sl, gl, c_edge, packed);
+                tmem_st16(lane_base + kColS + 128 * buf + 32 * hf, packed);
+                dq_half_finish<kF16>(sr, gr, c_edge, packed);
+                tmem_st16(lane_base + kColS + 128 * buf + 32 * hf + 16, packed);
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(&bars[A_DS_READY0 + buf]);
+                mbar_arrive(&bars[A_DS_READY]);
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 5);
             }
             if (!ok) break;
@@ -904,8 +922,8 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         encode_tile_map(&mq64, p.q.ptr, kind, D, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBK) ||
         encode_tile_map(&mdo64, p.d_o.ptr, kind, D, p.tokens, p.heads, B, p.d_o.stride_t, p.d_o.stride_h, p.d_o.stride_b, kBK))
         return 1;
-    // dq kernel: q, do, four k stages, three v stages; dk/dv kernel: k, v, early q / do, late q / do, p, ds, scalars
-    constexpr int need = 2 * kBM * D * 2 + (kDqKStages + kDqVStages) * kBK * D * 2 + 4096;
+    // dq kernel: q, do, three k stages, two v stages; dk/dv kernel: k, v, early q / do, late q / do, p, ds, scalars
+    constexpr int need = 2 * kBM * D * 2 + (kDqKStages + kDqVStages) * kBM * D * 2 + 3072;
     constexpr int need_b = 6 * kBM * D * 2 + 2 * 2 * 64 * 128 + 3072;
     constexpr int smem_a = need > 120 * 1024 ? need : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
     constexpr int smem_b = need_b > 120 * 1024 ? need_b : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
@@ -915,7 +933,7 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (p.bwd_phases != SBATTN_BWD_DKDV) tc_bwd_dq_kernel<D, kF16><<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk, mv, mdo, a);
+    if (p.bwd_phases != SBATTN_BWD_DKDV) tc_bwd_dq_kernel<D, kF16><<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk128, mv128, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, mq64, mdo64, a);
