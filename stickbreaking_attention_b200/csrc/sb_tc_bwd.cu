@@ -2,19 +2,19 @@
 // locks on dq, dk, dv (the reference accumulates dk/dv tiles in global memory under a spin lock,
 // stickbreaking_attention/sb_varlen/sb_varlen_bwd.py:11-53,454-465).
 //
-//   dq kernel     one work item = (head, sequence, 128-row query tile).  Walks the 64-key tiles LEFT TO RIGHT, the
-//                 direction of the reference's _backward_one_row (sb_varlen_bwd.py:401-473), because
+//   dq kernel     one work item = (head, sequence, 128-row query tile).  Walks the keys LEFT TO RIGHT in steps of 128,
+//                 the direction of the reference's _backward_one_row (sb_varlen_bwd.py:401-473), because
 //                 ds_ik = g_ik - beta_ik * (sum of g over keys <= k) needs a prefix over the keys.  The weights of a
-//                 tile need the product W of (1 - beta) over everything to its right: the forward saved that value
-//                 for every 64-key boundary (carry_w).  The kernel leaves the prefix of g through the right edge
-//                 of every tile in carry_c for the second kernel.
+//                 64-key half need the product W of (1 - beta) over everything to its right: the forward saved that
+//                 value for every 64-key boundary (carry_w).  The kernel leaves the prefix of g through the right
+//                 edge of every 64-key half in carry_c for the second kernel.
 //   dk/dv kernel  one work item = (head, sequence, 128-key tile), kept stationary; walks the 128-row query tiles
 //                 below it.  Every (query tile, 64-key half) pair is entered directly with carry_w and carry_c, the
 //                 weights and ds are recomputed, written to shared memory as 16-bit operands, and
-//                 dv^T += do^T p, dk^T += q^T ds accumulate in tensor memory for the whole walk; stored once.
+//                 dv += p^T do, dk += ds^T q accumulate in tensor memory for the whole walk; stored once.
 //
-// Both kernels: one persistent block per SM with 352 threads (warps 0-7: two groups of one thread per query row,
-// warps 8 and 10: TMA producers, warp 9: tcgen05.mma), all 512 tensor-memory columns, work drawn from a global counter.
+// Both kernels: one persistent block per SM (warps 0-7: two groups of one thread per query row, then TMA producers and
+// one warp that issues tcgen05.mma), all 512 tensor-memory columns, work drawn from a global counter.
 #include "sb_tc_common.cuh"
 
 namespace sb {
@@ -24,7 +24,7 @@ using namespace sm100;
 namespace {
 
 constexpr int kBM = 128;  // query rows per tile
-constexpr int kBK = 64;   // keys per tile
+constexpr int kBK = 64;   // keys per carry slot: carry_w / carry_c exist at every 64-key boundary
 constexpr int kQBox = 128 * 128;  // bytes of one TMA box of a 128-row tile (64 elements wide)
 constexpr int kKBox = 64 * 128;   // bytes of one TMA box of a 64-row tile
 
@@ -908,16 +908,13 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 template <int D, bool kF16>
 int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
-    CUtensorMap mq, mk, mv, mdo;
+    // Q, dO, K, V as 128-row tiles; the dk/dv kernel loads Q and dO also as 64-row halves
+    CUtensorMap mq, mdo, mk128, mv128, mq64, mdo64;
     const int kind = kF16 ? 2 : 0;
     const int64_t B = p.batch > 0 ? p.batch : 1;
     if (encode_tile_map(&mq, p.q.ptr, kind, D, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBM) ||
         encode_tile_map(&mdo, p.d_o.ptr, kind, D, p.tokens, p.heads, B, p.d_o.stride_t, p.d_o.stride_h, p.d_o.stride_b, kBM) ||
-        encode_tile_map(&mk, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBK) ||
-        encode_tile_map(&mv, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBK))
-        return 1;
-    CUtensorMap mk128, mv128, mq64, mdo64;  // the dk/dv kernel loads K and V as 128-row tiles, Q and dO also as 64-row halves
-    if (encode_tile_map(&mk128, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBM) ||
+        encode_tile_map(&mk128, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBM) ||
         encode_tile_map(&mv128, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBM) ||
         encode_tile_map(&mq64, p.q.ptr, kind, D, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBK) ||
         encode_tile_map(&mdo64, p.d_o.ptr, kind, D, p.tokens, p.heads, B, p.d_o.stride_t, p.d_o.stride_h, p.d_o.stride_b, kBK))
