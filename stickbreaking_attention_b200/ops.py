@@ -147,55 +147,162 @@ def _prep_cu(cu_seqlens, q, max_seqlens):
     return cu_seqlens, int(max_seqlens)
 
 
-def _forward(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad):
-    _require_cuda(q, k, v)
-    q, k, v = _unit_inner(q), _unit_inner(k), _unit_inner(v)
+def workspace_bytes(batched, n_seqs, heads, tokens, max_seqlens, save_carries=True):
+    """(forward, backward) workspace sizes in bytes: the formula of sbattn_workspace_bytes restated in Python, so that
+    a traced program (torch.compile) can size the buffers without calling into the library."""
+    tile = 128
+    up = lambda x: (x + 255) // 256 * 256
+    maxlen = tokens if batched else (min(max_seqlens, tokens) if max_seqlens > 0 else tokens)
+    n_max = max(1, (maxlen + tile - 1) // tile)
+    if batched:
+        max_items = n_seqs * n_max
+        slot_cap = n_seqs * n_max * (n_max + 1)
+    else:
+        max_items = tokens // tile + n_seqs
+        slot_cap = max_items * (n_max + 1)
+    off = 256                               # header
+    off = up(off + 16 * n_seqs)             # sequence table
+    off = up(off + 8 * max_items)           # item table
+    off = up(off + 4 * 2 * (n_max + 2))     # histogram scratch
+    carry = 4 * heads * slot_cap * tile
+    return off + (carry if save_carries else 0), up(carry)
+
+
+def _forward_into(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, o, rem, neg_log_acc,
+                  ws):
+    """The forward into buffers that exist already (what the registered operators do)."""
     with torch.cuda.device(q.device):
-        o = _empty_like_rows(q)
-        rem = torch.zeros(q.shape[:-1], dtype=q.dtype, device=q.device)
-        neg_log_acc = torch.zeros(q.shape[:-1], dtype=torch.float32, device=q.device)
         p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, not no_grad)
-        fwd_bytes, _ = _workspace_sizes(p)
-        ws = torch.empty(fwd_bytes, dtype=torch.uint8, device=q.device)
         p.q, p.k, p.v, p.o = _mat(q, batched), _mat(k, batched), _mat(v, batched), _mat(o, batched)
         p.rem, p.neg_log_acc = _vec(rem, batched), _vec(neg_log_acc, batched)
-        p.fwd_workspace, p.fwd_workspace_bytes = ws.data_ptr(), fwd_bytes
+        p.fwd_workspace, p.fwd_workspace_bytes = ws.data_ptr(), ws.numel()
         _lib.check(_lib.lib().sbattn_fwd(ctypes.byref(p)), "sbattn_fwd")
         if os.environ.get("SBATTN_CHECK_STATUS") == "1":
             check_status(q.device)
-    return o, rem, neg_log_acc, ws
 
 
-def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current, phases=0,
-              out=None, bwd_ws=None):
-    _require_cuda(q, k, v, do, dr, ws)
-    q, k, v, do = _unit_inner(q), _unit_inner(k), _unit_inner(v), _unit_inner(do)
-    if do.dtype != q.dtype:
-        do = do.to(q.dtype)
-    if dr.dtype != q.dtype:
-        dr = dr.to(q.dtype)
+def _backward_into(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current, phases, dq, dk,
+                   dv, bws):
     with torch.cuda.device(q.device):
-        if out is not None:
-            dq, dk, dv = out
-        else:
-            # no zero-fill: the library writes every row (rows outside all sequences are cleared by a small kernel)
-            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-            if dq.stride(-1) != 1:
-                dq, dk, dv = (torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
         p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, True)
         p.bwd_phases = phases
         fwd_bytes, bwd_bytes = _workspace_sizes(p)
         if ws.numel() < fwd_bytes:
             raise ValueError("the forward workspace does not belong to this problem (was the forward run with no_grad?)")
-        bws = bwd_ws if bwd_ws is not None else torch.empty(bwd_bytes, dtype=torch.uint8, device=q.device)
+        if bws.numel() < bwd_bytes:
+            raise ValueError("the backward workspace is too small")
         p.q, p.k, p.v = _mat(q, batched), _mat(k, batched), _mat(v, batched)
         p.d_o, p.d_rem = _mat(do, batched), _vec(dr, batched)
         p.dq, p.dk, p.dv = _mat(dq, batched), _mat(dk, batched), _mat(dv, batched)
         p.fwd_workspace, p.fwd_workspace_bytes = ws.data_ptr(), ws.numel()
-        p.bwd_workspace, p.bwd_workspace_bytes = bws.data_ptr(), bwd_bytes
+        p.bwd_workspace, p.bwd_workspace_bytes = bws.data_ptr(), bws.numel()
         _lib.check(_lib.lib().sbattn_bwd(ctypes.byref(p)), "sbattn_bwd")
         if os.environ.get("SBATTN_CHECK_STATUS") == "1":
             check_status(q.device)
+
+
+# ---------------------------------------------------------------------------------------------- registered operators
+# The reference wraps its launchers in torch.library.custom_op so that they survive torch.compile: operators
+# "stickbreaking_attention::varlen_fwd" / "varlen_bwd" / "attn_fwd" / "attn_bwd" that write into buffers allocated by the
+# caller and return None (utils.py:12-40, sb_varlen_fwd.py:453, sb_varlen_bwd.py:541, sb_fwd.py:175, sb_bwd.py:207).  The
+# same operators exist here, with this library's argument lists.  They take the reference's namespace unless the
+# reference itself has been imported into the process, in which case they go to "stickbreaking_attention_b200".
+def _register_ops():
+    ns = "stickbreaking_attention"
+    try:
+        getattr(torch.ops, ns).varlen_fwd
+        ns = "stickbreaking_attention_b200"
+    except (AttributeError, RuntimeError):
+        pass
+    T = torch.Tensor
+
+    @torch.library.custom_op(f"{ns}::varlen_fwd", mutates_args={"o", "rem", "neg_log_acc", "workspace"}, device_types="cuda")
+    def varlen_fwd_op(q: T, k: T, v: T, cu_seqlens: T, max_seqlens: int, logit_scale: float, attend_current: bool,
+                      no_grad: bool, o: T, rem: T, neg_log_acc: T, workspace: T) -> None:
+        _forward_into(q, k, v, False, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, o, rem, neg_log_acc,
+                      workspace)
+
+    @torch.library.custom_op(f"{ns}::varlen_bwd", mutates_args={"dq", "dk", "dv", "bwd_workspace"}, device_types="cuda")
+    def varlen_bwd_op(do: T, dr: T, q: T, k: T, v: T, cu_seqlens: T, max_seqlens: int, workspace: T, logit_scale: float,
+                      attend_current: bool, dq: T, dk: T, dv: T, bwd_workspace: T) -> None:
+        _backward_into(do, dr, q, k, v, False, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current, 0, dq, dk,
+                       dv, bwd_workspace)
+
+    @torch.library.custom_op(f"{ns}::attn_fwd", mutates_args={"o", "rem", "neg_log_acc", "workspace"}, device_types="cuda")
+    def attn_fwd_op(q: T, k: T, v: T, logit_scale: float, attend_current: bool, no_grad: bool, o: T, rem: T,
+                    neg_log_acc: T, workspace: T) -> None:
+        _forward_into(q, k, v, True, None, q.size(2), logit_scale, attend_current, no_grad, o, rem, neg_log_acc, workspace)
+
+    @torch.library.custom_op(f"{ns}::attn_bwd", mutates_args={"dq", "dk", "dv", "bwd_workspace"}, device_types="cuda")
+    def attn_bwd_op(do: T, dr: T, q: T, k: T, v: T, workspace: T, logit_scale: float, attend_current: bool, dq: T, dk: T,
+                    dv: T, bwd_workspace: T) -> None:
+        _backward_into(do, dr, q, k, v, True, None, q.size(2), workspace, logit_scale, attend_current, 0, dq, dk, dv,
+                       bwd_workspace)
+
+    return ns, {"varlen_fwd": varlen_fwd_op, "varlen_bwd": varlen_bwd_op, "attn_fwd": attn_fwd_op, "attn_bwd": attn_bwd_op}
+
+
+OP_NAMESPACE, _OPS = _register_ops()
+
+
+def _forward(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad):
+    compiling = torch.compiler.is_compiling()
+    if not compiling:
+        _require_cuda(q, k, v)
+    q, k, v = _unit_inner(q), _unit_inner(k), _unit_inner(v)
+    o = _empty_like_rows(q)
+    rem = torch.zeros(q.shape[:-1], dtype=q.dtype, device=q.device)
+    neg_log_acc = torch.zeros(q.shape[:-1], dtype=torch.float32, device=q.device)
+    if batched:
+        n_seqs, heads, tokens = q.size(0), q.size(1), q.size(2)
+    else:
+        n_seqs, heads, tokens = cu_seqlens.numel(), q.size(0), q.size(1)
+    fwd_bytes, _ = workspace_bytes(batched, n_seqs, heads, tokens, max_seqlens, not no_grad)
+    ws = torch.empty(fwd_bytes, dtype=torch.uint8, device=q.device)
+    if compiling:  # the traced program sees one opaque operator
+        if batched:
+            _OPS["attn_fwd"](q, k, v, float(logit_scale), bool(attend_current), bool(no_grad), o, rem, neg_log_acc, ws)
+        else:
+            _OPS["varlen_fwd"](q, k, v, cu_seqlens, int(max_seqlens), float(logit_scale), bool(attend_current),
+                               bool(no_grad), o, rem, neg_log_acc, ws)
+    else:
+        _forward_into(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, o, rem, neg_log_acc,
+                      ws)
+    return o, rem, neg_log_acc, ws
+
+
+def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current, phases=0,
+              out=None, bwd_ws=None):
+    compiling = torch.compiler.is_compiling()
+    if not compiling:
+        _require_cuda(q, k, v, do, dr, ws)
+    q, k, v, do = _unit_inner(q), _unit_inner(k), _unit_inner(v), _unit_inner(do)
+    if do.dtype != q.dtype:
+        do = do.to(q.dtype)
+    if dr.dtype != q.dtype:
+        dr = dr.to(q.dtype)
+    if out is not None:
+        dq, dk, dv = out
+    else:
+        # no zero-fill: the library writes every row (rows outside all sequences are cleared by a small kernel)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        if dq.stride(-1) != 1:
+            dq, dk, dv = (torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
+    if batched:
+        n_seqs, heads, tokens = q.size(0), q.size(1), q.size(2)
+    else:
+        n_seqs, heads, tokens = cu_seqlens.numel(), q.size(0), q.size(1)
+    _, bwd_bytes = workspace_bytes(batched, n_seqs, heads, tokens, max_seqlens)
+    bws = bwd_ws if bwd_ws is not None else torch.empty(bwd_bytes, dtype=torch.uint8, device=q.device)
+    if compiling:
+        if batched:
+            _OPS["attn_bwd"](do, dr, q, k, v, ws, float(logit_scale), bool(attend_current), dq, dk, dv, bws)
+        else:
+            _OPS["varlen_bwd"](do, dr, q, k, v, cu_seqlens, int(max_seqlens), ws, float(logit_scale), bool(attend_current),
+                               dq, dk, dv, bws)
+    else:
+        _backward_into(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current, phases, dq, dk,
+                       dv, bws)
     return dq, dk, dv
 
 

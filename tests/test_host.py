@@ -101,3 +101,35 @@ def test_product_never_imports_the_oracle():
         for f in files:
             if f.endswith((".py", ".cu", ".cuh")):
                 assert "oracle" not in open(os.path.join(dirpath, f)).read(), f
+
+
+def test_python_workspace_formula_matches_the_library(lib):
+    """The traced (torch.compile) path sizes its buffers in Python; the formula must agree with the library."""
+    from stickbreaking_attention_b200 import _lib, ops
+    for batched, n_seqs, heads, tokens, max_len in [(False, 3, 4, 512, 192), (False, 7, 32, 16384, 3696), (False, 1, 8, 65536, 65536),
+                                                     (False, 70, 64, 131072, 16384), (False, 5, 3, 1000, 0), (False, 2, 1, 77, 500),
+                                                     (True, 2, 4, 500, 500), (True, 1, 2, 128, 128), (True, 8, 16, 4096, 4096)]:
+        for save in (True, False):
+            p = _lib.SbParams()
+            p.dtype, p.heads, p.tokens, p.head_dim = _lib.SBATTN_BF16, heads, tokens, 64
+            p.batch = n_seqs if batched else 0
+            p.num_seqs = 0 if batched else n_seqs
+            p.cu_width = 4
+            p.max_seqlen = tokens if batched else max_len
+            p.save_carries = int(save)
+            fb, bb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+            assert lib.sbattn_workspace_bytes(ctypes.byref(p), ctypes.byref(fb), ctypes.byref(bb)) == 0
+            assert ops.workspace_bytes(batched, n_seqs, heads, tokens, max_len, save) == (fb.value, bb.value)
+
+
+def test_operators_are_registered_under_the_reference_names():
+    """stickbreaking_attention::{varlen,attn}_{fwd,bwd}: out-parameters mutated, nothing returned
+    (reference: utils.py:12-40, sb_varlen_fwd.py:453, sb_varlen_bwd.py:541, sb_fwd.py:175, sb_bwd.py:207)."""
+    from stickbreaking_attention_b200 import ops
+    ns = getattr(torch.ops, ops.OP_NAMESPACE)
+    assert ops.OP_NAMESPACE == "stickbreaking_attention"
+    for name, mutated in [("varlen_fwd", {"o", "rem", "neg_log_acc", "workspace"}), ("varlen_bwd", {"dq", "dk", "dv", "bwd_workspace"}),
+                          ("attn_fwd", {"o", "rem", "neg_log_acc", "workspace"}), ("attn_bwd", {"dq", "dk", "dv", "bwd_workspace"})]:
+        schema = getattr(ns, name).default._schema
+        assert {a.name for a in schema.arguments if a.alias_info is not None and a.alias_info.is_write} == mutated
+        assert len(schema.returns) == 0
