@@ -275,8 +275,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 ok = mbar_wait(&bars[A_QDO_FULL], items & 1, abort_flag);
                 if (!ok) break;
                 issue_s(G);
+                if (ok) issue_dp(G, n == 1);  // the row threads can start as soon as these two are complete
                 if (ok && n > 1) issue_s(G + 1);
-                if (ok) issue_dp(G, n == 1);
                 for (int j = 0; ok && j < n; ++j) {
                     const uint32_t g = G + j, kst = g % kDqKStages;
                     if (j + 1 < n) {  // dP of the next step as soon as this step's is in registers
@@ -412,18 +412,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 uint32_t v[32];
                 tmem_ld32(lane_base + kColDQ + d0 + cidx * 32, v);
                 tmem_wait_ld();
-                if (row_ok) {
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 u;
-                        uint32_t* up = (uint32_t*)&u;
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj)
-                            up[jj] = pack16<kF16>(__uint_as_float(v[q4 * 8 + 2 * jj]) * a.inv_temp,
-                                                  __uint_as_float(v[q4 * 8 + 2 * jj + 1]) * a.inv_temp);
-                        *(uint4*)(orow + (cidx * 32 + q4 * 8) * 2) = u;
-                    }
-                }
+                if (row_ok) store_row32<kF16>(orow + cidx * 64, v, a.inv_temp);
             }
             tc_fence_before();
             mbar_arrive(&bars[A_DQ_FREE]);
@@ -524,17 +513,7 @@ __device__ __noinline__ void kv_store_rows(const MatView m, float sc, const KvWo
         uint32_t v[32];
         tmem_ld32(taddr + cidx * 32, v);
         tmem_wait_ld();
-        if (key_ok) {
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                uint4 u;
-                uint32_t* up = (uint32_t*)&u;
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj)
-                    up[jj] = pack16<kF16>(__uint_as_float(v[q4 * 8 + 2 * jj]) * sc, __uint_as_float(v[q4 * 8 + 2 * jj + 1]) * sc);
-                *(uint4*)(orow + (cidx * 32 + q4 * 8) * 2) = u;
-            }
-        }
+        if (key_ok) store_row32<kF16>(orow + cidx * 64, v, sc);
     }
     tc_fence_before();
 }

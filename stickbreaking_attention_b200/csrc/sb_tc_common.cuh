@@ -47,6 +47,27 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     return kF16 ? sm100::pack_f16(lo, hi) : sm100::pack_bf16(lo, hi);
 }
 
+// 32 fp32 accumulator values of one row -> 32 16-bit values (64 bytes) at `dst`, scaled by `sc`.  256-bit stores where the
+// address allows it: every lane of a warp writes its own row, so each store instruction touches 32 different lines and
+// the number of instructions is what the epilogues cost.
+template <bool kF16>
+__device__ __forceinline__ void store_row32(char* dst, const uint32_t (&v)[32], float sc) {
+    uint32_t u[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) u[j] = pack16<kF16>(__uint_as_float(v[2 * j]) * sc, __uint_as_float(v[2 * j + 1]) * sc);
+    if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 32 * h), "r"(u[8 * h]),
+                         "r"(u[8 * h + 1]), "r"(u[8 * h + 2]), "r"(u[8 * h + 3]), "r"(u[8 * h + 4]), "r"(u[8 * h + 5]),
+                         "r"(u[8 * h + 6]), "r"(u[8 * h + 7])
+                         : "memory");
+    } else {
+#pragma unroll
+        for (int h = 0; h < 4; ++h) *(uint4*)(dst + 16 * h) = make_uint4(u[4 * h], u[4 * h + 1], u[4 * h + 2], u[4 * h + 3]);
+    }
+}
+
 // (head, sequence, 128-row tile) of a flat work index.  Order: groups of `head_group` heads; inside a group the
 // items heaviest first, the heads of the group innermost.
 struct Work {

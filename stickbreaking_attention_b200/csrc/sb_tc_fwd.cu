@@ -369,17 +369,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 uint32_t v[32];
                 tmem_ld32(lane_base + kColO + d0 + c * 32, v);
                 tmem_wait_ld();
-                if (row_ok) {
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint4 u;
-                        uint32_t* up = (uint32_t*)&u;
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj)
-                            up[jj] = pack16<kF16>(__uint_as_float(v[g * 8 + 2 * jj]), __uint_as_float(v[g * 8 + 2 * jj + 1]));
-                        *(uint4*)(orow + (c * 32 + g * 8) * 2) = u;
-                    }
-                }
+                if (row_ok) store_row32<kF16>(orow + c * 64, v, 1.f);
             }
             tc_fence_before();
             mbar_arrive(&bars[O_FREE]);
