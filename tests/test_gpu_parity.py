@@ -121,6 +121,32 @@ def test_strided_inputs_token_major():
     assert_close(NAMES, got, want, TOL_BF16)
 
 
+def test_outputs_at_16_byte_aligned_addresses():
+    """A C-ABI caller may hand over result buffers that are 16-byte but not 32-byte aligned (rows of D + 8 elements,
+    first column skipped): the epilogues then fall back from 256-bit to 128-bit stores.  Same bits as the dense call."""
+    from stickbreaking_attention_b200 import ops
+    lengths = [150, 300, 62]
+    H, T, D = 2, 512, 128
+    q, k, v, do, drem = (torch.from_numpy(x).cuda().bfloat16() for x in synth(H, T, D, seed=11))
+    cu = torch.tensor(np.cumsum(lengths), dtype=torch.int32, device="cuda")
+    scale = 1 / math.sqrt(D)
+    o, rem, nla, ws = ops.varlen_fwd(q, k, v, cu, max(lengths), scale)
+    dq, dk, dv = ops.varlen_bwd(do, drem, q, k, v, cu, max(lengths), ws, scale)
+    odd = lambda: torch.full((H, T, D + 8), 7.0, dtype=torch.bfloat16, device="cuda")[..., 8:]
+    o2, rem2, nla2 = odd(), torch.zeros_like(rem), torch.zeros_like(nla)
+    assert o2.data_ptr() % 32 == 16 and o2.stride(1) == D + 8
+    fb, bb = ops.workspace_bytes(False, cu.numel(), H, T, max(lengths))
+    ws2 = torch.empty(fb, dtype=torch.uint8, device="cuda")
+    ops._forward_into(q, k, v, False, cu, max(lengths), scale, False, False, o2, rem2, nla2, ws2)
+    dq2, dk2, dv2 = odd(), odd(), odd()
+    ops._backward_into(do, drem, q, k, v, False, cu, max(lengths), ws2, scale, False, 0, dq2, dk2, dv2,
+                       torch.empty(bb, dtype=torch.uint8, device="cuda"))
+    torch.cuda.synchronize()
+    ops.check_status()
+    for a_, b_ in [(o, o2), (rem, rem2), (dq, dq2), (dk, dk2), (dv, dv2)]:
+        assert torch.equal(a_, b_)
+
+
 def test_rows_sum_to_one_and_linearity_full_size():
     """Size-independent properties on the 16384-token benchmark pack: with v = 1 every o entry equals 1 - rem,
     and o is linear in v."""
