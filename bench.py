@@ -173,12 +173,12 @@ def cpu_reference_step(wl, heads, seqs, seed=0):
 def cpu_sample_of(wl):
     """A sample of the workload the host finishes in roughly 10-30 s: one head, sequences capped at 4096 tokens."""
     seqs = [min(l, 4096) for l in wl["lengths"]]
-    budget, out = 6.0e10 * 3, []   # sum of L^3 the sample may hold
+    room, out = 6.0e10 * 3, []   # sum of L^3 the sample may hold
     for l in seqs:
-        if budget - float(l) ** 3 < 0 and out:
+        if room - float(l) ** 3 < 0 and out:
             break
         out.append(l)
-        budget -= float(l) ** 3
+        room -= float(l) ** 3
     return out
 
 

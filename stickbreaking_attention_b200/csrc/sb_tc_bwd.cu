@@ -426,8 +426,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
 // ================================================================================================ dk/dv kernel
 // One block per SM (384 threads) keeps a 128-key tile stationary and walks the 128-row query tiles below it.  All four
-// contractions run with M = 128 and N = 128 (N = D for the last two), the widest shape the tensor-memory budget
-// allows: S and dP [128 q x 128 keys], dv and dk [128 keys x D] (an MMA instruction costs the same ~65 cycles for N = 64
+// contractions run with M = 128 and N = 128 (N = D for the last two), the widest shape that 512 columns of tensor
+// memory allow: S and dP [128 q x 128 keys], dv and dk [128 keys x D] (an MMA instruction costs the same ~65 cycles for N = 64
 // and N = 128, so narrow tiles waste half of the tensor pipe).  Tensor memory is full with these four, so S and dP cannot
 // be double-buffered; the step is pipelined another way:
 //   * a row thread copies its 64 scores and 64 dP values to registers as soon as they exist and releases S / dP at once,

@@ -54,7 +54,9 @@ def run_case(stickbreaking, spec):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of speedcell4/stickbreaking-attention>")
+    root = sys.argv[1]
     stickbreaking = load_reference(root)
     torch.manual_seed(0)
     for name, spec in CASES.items():
