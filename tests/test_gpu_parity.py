@@ -248,3 +248,36 @@ def test_tokens_outside_all_sequences_get_zero_gradients():
     want = oracle_varlen(q[:, :280], k[:, :280], v[:, :280], do[:, :280], drem[:, :280], lengths, 1 / math.sqrt(D), False)
     got = [x.detach().double().cpu().numpy()[:, :280] for x in (o, rem, dq, dk, dv)]
     assert_close(NAMES, got, want, TOL_BF16)
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_tensor_path_agrees_with_fp32_arithmetic_path_on_random_packs(seed):
+    """Random ragged packs (many short sequences next to long ones, both head dims, both 16-bit types, both
+    diagonal conventions): the tcgen05 kernels against the fp32-arithmetic kernels of the same library on the same
+    16-bit inputs.  Sized beyond what the numpy oracle finishes quickly; exercises item transitions of the
+    persistent kernels (sequences of 1 ... 3 tiles) and several items per block."""
+    from stickbreaking_attention_b200 import get_path, sb_attn_varlen, set_path
+    rng = np.random.default_rng(seed)
+    D = [64, 128][seed % 2]
+    dtype = [torch.bfloat16, torch.float16][(seed // 2) % 2]
+    attend_current = bool(seed % 2)
+    lengths = [int(x) for x in rng.integers(1, 400, size=40)] + [1500, 129, 128, 127, 1, 2600]
+    H, T = 5, sum(lengths)
+    g = torch.Generator().manual_seed(seed)
+    q, k, v, do = (torch.randn(H, T, D, generator=g).to("cuda", dtype) for _ in range(4))
+    dr = torch.randn(H, T, generator=g).to("cuda", dtype)
+    cu = torch.tensor(np.cumsum(lengths), dtype=torch.int32, device="cuda")
+    res = {}
+    old = get_path()
+    try:
+        for path in ("tensor", "simt"):
+            set_path(path)
+            tq, tk, tv = (x.clone().requires_grad_() for x in (q, k, v))
+            o, rem = sb_attn_varlen(tq, tk, tv, cu, max(lengths), zero_start=False, attend_current=attend_current)
+            res[path] = [x.detach().float() for x in (o, rem) + torch.autograd.grad([o, rem], [tq, tk, tv], [do, dr])]
+    finally:
+        set_path(old)
+    # both sides are rounded to 16 bits on output: allow one unit in the last place of bfloat16 on top of the bar
+    for name, a_, b_ in zip(NAMES, res["tensor"], res["simt"]):
+        excess = ((a_ - b_).abs() - (TOL_BF16 + b_.abs() * 2.0 ** -7)).max().item()
+        assert excess <= 0, (name, excess)
