@@ -69,6 +69,13 @@ typedef struct SbVec {
     int64_t stride_b, stride_h, stride_t;
 } SbVec;
 
+/* SbParams::flags.  SBATTN_FLAG_FUSED_REMAINDER: the forward writes out = o + rem * v into `o` (what every caller of the
+ * reference computes next: tests/test_varlen.py:103, tests/test_attn.py:67, benchmarks/varlen.py:53), with rem rounded
+ * to the output dtype first, as in that expression.  The backward then takes d_o = gradient of out and d_rem = gradient
+ * of the separately returned rem, needs `rem` (the forward's output) and `v`, and returns dv including rem * d_o.
+ * Tensor-core path only (16-bit inputs, head_dim 64 or 128): otherwise SBATTN_EUNSUPPORTED. */
+#define SBATTN_FLAG_FUSED_REMAINDER 1
+
 typedef struct SbParams {
     int32_t dtype;          /* SBATTN_BF16 / F32 / F16                                                    */
     int32_t path;           /* SBATTN_PATH_*                                                              */
@@ -85,7 +92,7 @@ typedef struct SbParams {
     int32_t save_carries;   /* forward: 1 if a backward will follow (fills the carry part of fwd_workspace) */
     int32_t bwd_phases;     /* backward: 0 = everything; SBATTN_BWD_DQ / SBATTN_BWD_DKDV run one kernel only
                                (for timing them apart; dk/dv needs the carries the dq kernel leaves behind)   */
-    int32_t reserved;
+    int32_t flags;          /* SBATTN_FLAG_*                                                              */
 
     SbMat q, k, v;          /* inputs                                                                     */
     SbMat o;                /* forward output, dtype                                                      */

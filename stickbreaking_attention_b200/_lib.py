@@ -27,7 +27,7 @@ class SbParams(ctypes.Structure):
         ("tokens", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("num_seqs", ctypes.c_int32),
         ("cu_width", ctypes.c_int32), ("cu_seqlens", ctypes.c_void_p), ("max_seqlen", ctypes.c_int32),
         ("attend_current", ctypes.c_int32), ("inv_temp", ctypes.c_float), ("save_carries", ctypes.c_int32),
-        ("bwd_phases", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("bwd_phases", ctypes.c_int32), ("flags", ctypes.c_int32),
         ("q", SbMat), ("k", SbMat), ("v", SbMat), ("o", SbMat), ("rem", SbVec), ("neg_log_acc", SbVec),
         ("d_o", SbMat), ("d_rem", SbVec), ("dq", SbMat), ("dk", SbMat), ("dv", SbMat),
         ("fwd_workspace", ctypes.c_void_p), ("fwd_workspace_bytes", ctypes.c_size_t),
@@ -35,6 +35,8 @@ class SbParams(ctypes.Structure):
         ("status", ctypes.c_void_p), ("stream", ctypes.c_void_p),
     ]
 
+
+FLAG_FUSED_REMAINDER = 1
 
 EXPORTS = ("sbattn_workspace_bytes", "sbattn_fwd", "sbattn_bwd", "sbattn_strerror", "sbattn_version",
            "sbattn_params_size", "sbattn_fwd_static", "sbattn_static_scratch_bytes")

@@ -46,6 +46,10 @@ KArgs make_args(const SbParams& p, const WsLayout& L) {
     a.items = (const int2*)(ws + L.off_items);
     a.carry_w = p.save_carries ? (float*)(ws + L.off_carry) : nullptr;
     a.carry_c = (float*)p.bwd_workspace;
+    a.drem_eff = p.bwd_workspace ? (float*)((char*)p.bwd_workspace + L.off_drem) : nullptr;
+    a.fused = (p.flags & SBATTN_FLAG_FUSED_REMAINDER) ? 1 : 0;
+    a.tokens = p.tokens;
+    a.drem_rows = (int64_t)p.tokens * (p.batch > 0 ? p.batch : 1);
     a.slot_cap = L.slot_cap;
     a.heads = p.heads;
     a.head_dim = p.head_dim;
@@ -120,6 +124,7 @@ extern "C" int sbattn_fwd(const SbParams* p) {
     if (((uintptr_t)p->fwd_workspace & 255) != 0) return SBATTN_EWORKSPACE;
     const int path = choose_path(*p, false);
     if (path < 0) return path;
+    if ((p->flags & SBATTN_FLAG_FUSED_REMAINDER) && path != 1) return SBATTN_EUNSUPPORTED;  // tensor-core kernels only
     cudaStream_t st = (cudaStream_t)p->stream;
     if (launch_prep(*p, L, st) != 0) return SBATTN_ECUDA;
     const KArgs a = make_args(*p, L);
@@ -143,6 +148,10 @@ extern "C" int sbattn_bwd(const SbParams* p) {
     if (((uintptr_t)p->fwd_workspace & 255) != 0 || ((uintptr_t)p->bwd_workspace & 255) != 0) return SBATTN_EWORKSPACE;
     const int path = choose_path(*p, true);
     if (path < 0) return path;
+    if (p->flags & SBATTN_FLAG_FUSED_REMAINDER) {
+        if (path != 1) return SBATTN_EUNSUPPORTED;
+        if ((rc = check_vec(p->rem, true))) return rc;  // the forward's rem: dv includes rem * d_o
+    }
     cudaStream_t st = (cudaStream_t)p->stream;
     const KArgs a = make_args(*p, L);
     if (p->bwd_phases == SBATTN_BWD_ALL && launch_zero_tail(*p, a, st) != 0) return SBATTN_ECUDA;

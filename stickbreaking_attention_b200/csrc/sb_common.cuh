@@ -45,6 +45,7 @@ struct WsLayout {
     int64_t slot_cap;    // upper bound on carry slots per head
     int32_t hb;          // heads (batched: heads; the batch index comes from the sequence)
     size_t off_seqs, off_items, off_bins, off_carry;
+    size_t off_drem;     // inside the backward workspace
     size_t fwd_bytes;    // with carries if save_carries
     size_t bwd_bytes;
 };
@@ -78,7 +79,8 @@ inline WsLayout make_layout(const SbParams& p) {
     L.off_carry = off;
     const size_t carry = sizeof(float) * (size_t)L.hb * (size_t)L.slot_cap * kTileQ;
     L.fwd_bytes = off + (p.save_carries ? carry : 0);
-    L.bwd_bytes = align_up(carry, 256);
+    L.off_drem = align_up(carry, 256);  // after carry_c: drem + do . v per (head, token), fused-remainder backward
+    L.bwd_bytes = L.off_drem + align_up(sizeof(float) * (size_t)p.heads * (size_t)p.tokens * (size_t)(batched ? p.batch : 1), 256);
     return L;
 }
 
@@ -103,6 +105,10 @@ struct KArgs {
     float* carry_c;         // backward carries [heads][slot_cap][128]
     int64_t slot_cap;
     int32_t heads, head_dim, attend_current;
+    int32_t fused;          // SBATTN_FLAG_FUSED_REMAINDER
+    int32_t tokens;         // tokens per batch entry (row index of drem_eff: batch * tokens + token)
+    float* drem_eff;        // [heads][drem_rows]: drem + do . v, written by the dq kernel when fused
+    int64_t drem_rows;      // batch * tokens (tokens for the packed layout)
     int32_t head_group;     // heads whose work is interleaved (sized so that their K and V stay in L2)
     int32_t* sched;         // WsHeader::sched
     float inv_temp;

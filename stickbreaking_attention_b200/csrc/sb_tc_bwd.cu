@@ -122,7 +122,9 @@ __device__ __forceinline__ void dq_half_finish(const uint32_t (&beta)[32], const
     }
 }
 
-template <int D, bool kF16>
+// kFused (both backward kernels): d_o is the gradient of out = o + rem * v; separate instantiations, the plain ones stay
+// as they are
+template <int D, bool kF16, bool kFused>
 __global__ void __launch_bounds__(kDqThreads, 1)
 tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const KArgs a) {
@@ -333,6 +335,22 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh + tok * a.d_rem.st);
                 drem = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
             }
+            if (kFused && row_ok) {
+                // rem also receives do . v; the sum is left for the dk/dv kernel
+                const char* dorow = a.d_o.ptr + 2 * ((int64_t)wk.b * a.d_o.sb + (int64_t)wk.h * a.d_o.sh + tok * a.d_o.st);
+                const char* vrow = a.v.ptr + 2 * ((int64_t)wk.b * a.v.sb + (int64_t)wk.h * a.v.sh + tok * a.v.st);
+                float dot = 0.f;
+#pragma unroll
+                for (int cidx = 0; cidx < D / 32; ++cidx) {
+                    float x[32], y[32];
+                    load_row32<kF16>(dorow + cidx * 64, x);
+                    load_row32<kF16>(vrow + cidx * 64, y);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) dot = fmaf(x[i], y[i], dot);
+                }
+                drem += dot;
+                if (grp == 0) a.drem_eff[(int64_t)wk.h * a.drem_rows + (int64_t)wk.b * a.tokens + wk.start + qi] = drem;
+            }
             const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             // the carry of a step is copied to shared memory one step ahead (cp.async): held in a register it would be
@@ -503,26 +521,48 @@ __device__ __forceinline__ void kv_chunk(const uint32_t (&s)[32], const uint32_t
 
 // dk or dv of a finished item out of tensor memory: a thread holds one key row, the head dim along the columns.
 // Not inlined: it runs once per item, and inside the step loop it would only dilute the instruction cache.
-template <int D, bool kF16>
-__device__ __noinline__ void kv_store_rows(const MatView m, float sc, const KvWork e, int r, uint32_t taddr) {
+// With the fused remainder dv also receives rem * do of its own row: the direct path of out = o + rem * v.
+template <int D, bool kF16, bool kFused>
+__device__ __noinline__ void kv_store_rows(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr) {
     tc_fence_after();
+    const MatView m = is_dv ? a.dv : a.dk;
+    const float sc = is_dv ? 1.f : a.inv_temp;
     const bool key_ok = e.kt * kKT + r < e.len;
-    char* orow = m.ptr + 2 * ((int64_t)e.b * m.sb + (int64_t)e.h * m.sh + (int64_t)(e.start + e.kt * kKT + r) * m.st);
+    const int64_t tok = e.start + e.kt * kKT + r;
+    char* orow = m.ptr + 2 * ((int64_t)e.b * m.sb + (int64_t)e.h * m.sh + tok * m.st);
+    const char* add = nullptr;
+    float mul = 0.f;
+    if (kFused && is_dv && key_ok) {
+        add = a.d_o.ptr + 2 * ((int64_t)e.b * a.d_o.sb + (int64_t)e.h * a.d_o.sh + tok * a.d_o.st);
+        const char* rp = a.rem.ptr + 2 * ((int64_t)e.b * a.rem.sb + (int64_t)e.h * a.rem.sh + tok * a.rem.st);
+        mul = kF16 ? __half2float(*(const __half*)rp) : __bfloat162float(*(const __nv_bfloat16*)rp);
+    }
 #pragma unroll
     for (int cidx = 0; cidx < D / 32; ++cidx) {
         uint32_t v[32];
         tmem_ld32(taddr + cidx * 32, v);
         tmem_wait_ld();
-        if (key_ok) store_row32<kF16>(orow + cidx * 64, v, sc);
+        if (key_ok) {
+            if (kFused && add) {
+                float x[32];
+                load_row32<kF16>(add + cidx * 64, x);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(fmaf(mul, x[i], __uint_as_float(v[i])));
+                store_row32<kF16>(orow + cidx * 64, v, 1.f);
+            } else {
+                store_row32<kF16>(orow + cidx * 64, v, sc);
+            }
+        }
     }
     tc_fence_before();
 }
 
-template <int D, bool kF16>
+template <int D, bool kF16, bool kFused>
 __global__ void __launch_bounds__(kKvThreads, 1)
 tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                   const __grid_constant__ CUtensorMap map_q64, const __grid_constant__ CUtensorMap map_do64, const KArgs a) {
+                   const __grid_constant__ CUtensorMap map_q64, const __grid_constant__ CUtensorMap map_do64,
+                   const __grid_constant__ KArgs a) {
     constexpr int kBoxes = D / 64;
     constexpr int kQBytes = kBM * D * 2;     // a 128-row tile of Q, dO, K or V
     constexpr int kHalfBytes = kQBytes / 2;  // 64 rows of Q or dO: kBoxes boxes of kKBox bytes
@@ -655,7 +695,9 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     const int r = m * 32 + lane, qi = i * kBM + r;
                     const bool row_ok = qi < wk.len;
                     vd[m] = 0.f;
-                    if (row_ok) {
+                    if (kFused) {  // drem + do . v, left behind by the dq kernel
+                        if (row_ok) vd[m] = a.drem_eff[(int64_t)wk.h * a.drem_rows + (int64_t)wk.b * a.tokens + wk.start + qi];
+                    } else if (row_ok) {
                         const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh +
                                                             (int64_t)(wk.start + qi) * a.d_rem.st);
                         vd[m] = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
@@ -806,8 +848,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             ok = mbar_wait(&bars[B_DKV_READY], item & 1, abort_flag);
             if (!ok) return;
             if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 6);
-            kv_store_rows<D, kF16>(grp == 0 ? a.dk : a.dv, grp == 0 ? a.inv_temp : 1.f, e, r,
-                                   lane_base + (grp == 0 ? kColDK : kColDV));
+            kv_store_rows<D, kF16, kFused>(a, grp == 1, e, r, lane_base + (grp == 0 ? kColDK : kColDV));
             mbar_arrive(&bars[B_DKV_FREE]);
             if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 7);
         };
@@ -885,6 +926,25 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     sched_finish(a.sched + 4);
 }
 
+template <int D, bool kF16, bool kFused>
+int launch_bwd_kernels(const SbParams& p, const KArgs& a, cudaStream_t st, const CUtensorMap& mq, const CUtensorMap& mk128,
+                       const CUtensorMap& mv128, const CUtensorMap& mdo, const CUtensorMap& mq64, const CUtensorMap& mdo64,
+                       int smem_a, int smem_b) {
+    cudaError_t e = cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16, kFused>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16, kFused>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_b);
+    if (e != cudaSuccess) return (int)e;
+    cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16, kFused>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16, kFused>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (p.bwd_phases != SBATTN_BWD_DKDV)
+        tc_bwd_dq_kernel<D, kF16, kFused><<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk128, mv128, mdo, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (p.bwd_phases != SBATTN_BWD_DQ)
+        tc_bwd_dkdv_kernel<D, kF16, kFused><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, mq64, mdo64, a);
+    return (int)cudaGetLastError();
+}
+
 template <int D, bool kF16>
 int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     // Q, dO, K, V as 128-row tiles; the dk/dv kernel loads Q and dO also as 64-row halves
@@ -903,17 +963,8 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     constexpr int need_b = 6 * kBM * D * 2 + 2 * 2 * 64 * 128 + 3072;
     constexpr int smem_a = need > 120 * 1024 ? need : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
     constexpr int smem_b = need_b > 120 * 1024 ? need_b : 120 * 1024;  // one block per SM: it owns all 512 tensor-memory columns
-    cudaError_t e = cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_b);
-    if (e != cudaSuccess) return (int)e;
-    cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (p.bwd_phases != SBATTN_BWD_DKDV) tc_bwd_dq_kernel<D, kF16><<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk128, mv128, mdo, a);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return (int)e;
-    if (p.bwd_phases != SBATTN_BWD_DQ) tc_bwd_dkdv_kernel<D, kF16><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, mq64, mdo64, a);
-    return (int)cudaGetLastError();
+    return a.fused ? launch_bwd_kernels<D, kF16, true>(p, a, st, mq, mk128, mv128, mdo, mq64, mdo64, smem_a, smem_b)
+                   : launch_bwd_kernels<D, kF16, false>(p, a, st, mq, mk128, mv128, mdo, mq64, mdo64, smem_a, smem_b);
 }
 
 }  // namespace

@@ -68,6 +68,31 @@ __device__ __forceinline__ void store_row32(char* dst, const uint32_t (&v)[32], 
     }
 }
 
+// 32 16-bit values at `src` as fp32
+template <bool kF16>
+__device__ __forceinline__ void load_row32(const char* src, float (&x)[32]) {
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        const uint4 u = __ldg((const uint4*)(src + 16 * h));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (kF16) {
+                const float2 f = __half22float2(*(const __half2*)&w[j]);
+                x[8 * h + 2 * j] = f.x;
+                x[8 * h + 2 * j + 1] = f.y;
+            } else {
+                x[8 * h + 2 * j] = __uint_as_float(w[j] << 16);
+                x[8 * h + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            }
+        }
+    }
+}
+template <bool kF16>
+__device__ __forceinline__ float round16(float x) {
+    return kF16 ? __half2float(__float2half_rn(x)) : __bfloat162float(__float2bfloat16_rn(x));
+}
+
 // (head, sequence, 128-row tile) of a flat work index.  Order: groups of `head_group` heads; inside a group the
 // items heaviest first, the heads of the group innermost.
 struct Work {

@@ -84,7 +84,8 @@ __device__ __forceinline__ void fwd_finish(const uint32_t (&s)[32], const float*
     }
 }
 
-template <int D, bool kF16>
+// kFused: out = o + rem * v is formed in the epilogue (a separate instantiation: the plain one stays as it is)
+template <int D, bool kF16, bool kFused>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const KArgs a) {
@@ -101,6 +102,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     uint32_t* tmem_slot = (uint32_t*)(ring + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* xw = (float*)(tmem_slot + 4);  // [group][128 rows]: carry leaving the tile the group has just swept
+    float* wfin = xw + 256;               // [item parity][128 rows]: remainder of the row, for the fused epilogue of both groups
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -278,7 +280,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const float scale = a.inv_temp * kLog2e;
         float* x_mine = xw + b * 128;
         const float* x_other = xw + (b ^ 1) * 128;
-        uint32_t ph_o = 0, ph_x = 0;
+        uint32_t ph_o = 0, ph_x = 0, items = 0;
         bool ok = true;
         SB_TRACE_DECL(c);
         SchedConsumer sched;
@@ -336,6 +338,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 if (j + 1 < n) {
                     x_mine[r] = W;
                     mbar_arrive(&bars[X_W0 + b]);
+                } else if (kFused) {
+                    wfin[(items & 1) * 128 + r] = W;  // visible to both groups once O_READY has completed
                 }
                 if (r == 0) SB_TRACE_EV(c, 1 + b, 4);
                 if (cw) {
@@ -369,10 +373,21 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 uint32_t v[32];
                 tmem_ld32(lane_base + kColO + d0 + c * 32, v);
                 tmem_wait_ld();
-                if (row_ok) store_row32<kF16>(orow + c * 64, v, 1.f);
+                if (row_ok) {
+                    if (kFused) {  // out = o + rem * v, rem rounded to the output type first
+                        const float remf = round16<kF16>(wfin[(items & 1) * 128 + r]);
+                        float x[32];
+                        load_row32<kF16>(a.v.ptr + 2 * ((int64_t)wk.b * a.v.sb + (int64_t)wk.h * a.v.sh +
+                                                         (int64_t)(wk.start + qi) * a.v.st + d0) + c * 64, x);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(fmaf(remf, x[i], __uint_as_float(v[i])));
+                    }
+                    store_row32<kF16>(orow + c * 64, v, 1.f);
+                }
             }
             tc_fence_before();
             mbar_arrive(&bars[O_FREE]);
+            ++items;
             if (row_ok && ((n - 1) & 1) == b) {  // this group swept the leftmost tile: W is the remainder of the row
                 const int64_t t = wk.start + qi;
                 char* rp = a.rem.ptr + 2 * ((int64_t)wk.b * a.rem.sb + (int64_t)wk.h * a.rem.sh + t * a.rem.st);
@@ -396,11 +411,17 @@ int launch_fwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         encode_tile_map(&mv, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBN))
         return 1;
     // Q + three K stages + two V stages; at least 120 KB so that one block owns the SM and its tensor memory
-    constexpr int need = (1 + kKStages + kVStages) * kBM * D * 2 + 1024 + 2048;
+    constexpr int need = (1 + kKStages + kVStages) * kBM * D * 2 + 1024 + 3072;
     constexpr int smem = need > 120 * 1024 ? need : 120 * 1024;
-    cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (a.fused) {
+        cudaError_t ef = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (ef != cudaSuccess) return (int)ef;
+        tc_fwd_kernel<D, kF16, true><<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
+        return (int)cudaGetLastError();
+    }
+    cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    tc_fwd_kernel<D, kF16><<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
+    tc_fwd_kernel<D, kF16, false><<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
     return (int)cudaGetLastError();
 }
 

@@ -86,7 +86,7 @@ def _empty_like_rows(t):
     return out if out.stride(-1) == 1 else torch.empty(t.shape, dtype=t.dtype, device=t.device)
 
 
-def _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, save_carries):
+def _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, save_carries, fused=False):
     if q.dtype not in _DTYPES:
         raise TypeError(f"unsupported dtype {q.dtype}")
     p = SbParams()
@@ -106,6 +106,7 @@ def _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_curren
     p.attend_current = int(bool(attend_current))
     p.inv_temp = float(logit_scale)
     p.save_carries = int(bool(save_carries))
+    p.flags = _lib.FLAG_FUSED_REMAINDER if fused else 0
     p.status = status_word(q.device).data_ptr()
     p.stream = torch.cuda.current_stream(q.device).cuda_stream
     return p
@@ -165,14 +166,15 @@ def workspace_bytes(batched, n_seqs, heads, tokens, max_seqlens, save_carries=Tr
     off = up(off + 8 * max_items)           # item table
     off = up(off + 4 * 2 * (n_max + 2))     # histogram scratch
     carry = 4 * heads * slot_cap * tile
-    return off + (carry if save_carries else 0), up(carry)
+    drem = 4 * heads * tokens * (n_seqs if batched else 1)  # drem + do . v per row (fused-remainder backward)
+    return off + (carry if save_carries else 0), up(carry) + up(drem)
 
 
 def _forward_into(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, o, rem, neg_log_acc,
-                  ws):
+                  ws, fused=False):
     """The forward into buffers that exist already (what the registered operators do)."""
     with torch.cuda.device(q.device):
-        p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, not no_grad)
+        p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, not no_grad, fused)
         p.q, p.k, p.v, p.o = _mat(q, batched), _mat(k, batched), _mat(v, batched), _mat(o, batched)
         p.rem, p.neg_log_acc = _vec(rem, batched), _vec(neg_log_acc, batched)
         p.fwd_workspace, p.fwd_workspace_bytes = ws.data_ptr(), ws.numel()
@@ -182,9 +184,11 @@ def _forward_into(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend
 
 
 def _backward_into(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current, phases, dq, dk,
-                   dv, bws):
+                   dv, bws, fused=False, rem=None):
     with torch.cuda.device(q.device):
-        p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, True)
+        p = _base_params(q, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, True, fused)
+        if fused:
+            p.rem = _vec(rem, batched)
         p.bwd_phases = phases
         fwd_bytes, bwd_bytes = _workspace_sizes(p)
         if ws.numel() < fwd_bytes:
@@ -218,26 +222,27 @@ def _register_ops():
 
     @torch.library.custom_op(f"{ns}::varlen_fwd", mutates_args={"o", "rem", "neg_log_acc", "workspace"}, device_types="cuda")
     def varlen_fwd_op(q: T, k: T, v: T, cu_seqlens: T, max_seqlens: int, logit_scale: float, attend_current: bool,
-                      no_grad: bool, o: T, rem: T, neg_log_acc: T, workspace: T) -> None:
+                      no_grad: bool, fused: bool, o: T, rem: T, neg_log_acc: T, workspace: T) -> None:
         _forward_into(q, k, v, False, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, o, rem, neg_log_acc,
-                      workspace)
+                      workspace, fused)
 
     @torch.library.custom_op(f"{ns}::varlen_bwd", mutates_args={"dq", "dk", "dv", "bwd_workspace"}, device_types="cuda")
     def varlen_bwd_op(do: T, dr: T, q: T, k: T, v: T, cu_seqlens: T, max_seqlens: int, workspace: T, logit_scale: float,
-                      attend_current: bool, dq: T, dk: T, dv: T, bwd_workspace: T) -> None:
+                      attend_current: bool, fused: bool, rem: T, dq: T, dk: T, dv: T, bwd_workspace: T) -> None:
         _backward_into(do, dr, q, k, v, False, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current, 0, dq, dk,
-                       dv, bwd_workspace)
+                       dv, bwd_workspace, fused, rem)
 
     @torch.library.custom_op(f"{ns}::attn_fwd", mutates_args={"o", "rem", "neg_log_acc", "workspace"}, device_types="cuda")
-    def attn_fwd_op(q: T, k: T, v: T, logit_scale: float, attend_current: bool, no_grad: bool, o: T, rem: T,
+    def attn_fwd_op(q: T, k: T, v: T, logit_scale: float, attend_current: bool, no_grad: bool, fused: bool, o: T, rem: T,
                     neg_log_acc: T, workspace: T) -> None:
-        _forward_into(q, k, v, True, None, q.size(2), logit_scale, attend_current, no_grad, o, rem, neg_log_acc, workspace)
+        _forward_into(q, k, v, True, None, q.size(2), logit_scale, attend_current, no_grad, o, rem, neg_log_acc, workspace,
+                      fused)
 
     @torch.library.custom_op(f"{ns}::attn_bwd", mutates_args={"dq", "dk", "dv", "bwd_workspace"}, device_types="cuda")
-    def attn_bwd_op(do: T, dr: T, q: T, k: T, v: T, workspace: T, logit_scale: float, attend_current: bool, dq: T, dk: T,
-                    dv: T, bwd_workspace: T) -> None:
+    def attn_bwd_op(do: T, dr: T, q: T, k: T, v: T, workspace: T, logit_scale: float, attend_current: bool, fused: bool,
+                    rem: T, dq: T, dk: T, dv: T, bwd_workspace: T) -> None:
         _backward_into(do, dr, q, k, v, True, None, q.size(2), workspace, logit_scale, attend_current, 0, dq, dk, dv,
-                       bwd_workspace)
+                       bwd_workspace, fused, rem)
 
     return ns, {"varlen_fwd": varlen_fwd_op, "varlen_bwd": varlen_bwd_op, "attn_fwd": attn_fwd_op, "attn_bwd": attn_bwd_op}
 
@@ -245,7 +250,7 @@ def _register_ops():
 OP_NAMESPACE, _OPS = _register_ops()
 
 
-def _forward(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad):
+def _forward(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, fused=False):
     compiling = torch.compiler.is_compiling()
     if not compiling:
         _require_cuda(q, k, v)
@@ -261,18 +266,21 @@ def _forward(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_curr
     ws = torch.empty(fwd_bytes, dtype=torch.uint8, device=q.device)
     if compiling:  # the traced program sees one opaque operator
         if batched:
-            _OPS["attn_fwd"](q, k, v, float(logit_scale), bool(attend_current), bool(no_grad), o, rem, neg_log_acc, ws)
+            _OPS["attn_fwd"](q, k, v, float(logit_scale), bool(attend_current), bool(no_grad), bool(fused), o, rem,
+                             neg_log_acc, ws)
         else:
             _OPS["varlen_fwd"](q, k, v, cu_seqlens, int(max_seqlens), float(logit_scale), bool(attend_current),
-                               bool(no_grad), o, rem, neg_log_acc, ws)
+                               bool(no_grad), bool(fused), o, rem, neg_log_acc, ws)
     else:
         _forward_into(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, o, rem, neg_log_acc,
-                      ws)
+                      ws, fused)
     return o, rem, neg_log_acc, ws
 
 
 def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current, phases=0,
-              out=None, bwd_ws=None):
+              out=None, bwd_ws=None, fused=False, rem=None):
+    if rem is None:
+        rem = dr  # placeholder of the right shape: only read when fused
     compiling = torch.compiler.is_compiling()
     if not compiling:
         _require_cuda(q, k, v, do, dr, ws)
@@ -296,43 +304,52 @@ def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale
     bws = bwd_ws if bwd_ws is not None else torch.empty(bwd_bytes, dtype=torch.uint8, device=q.device)
     if compiling:
         if batched:
-            _OPS["attn_bwd"](do, dr, q, k, v, ws, float(logit_scale), bool(attend_current), dq, dk, dv, bws)
+            _OPS["attn_bwd"](do, dr, q, k, v, ws, float(logit_scale), bool(attend_current), bool(fused), rem, dq, dk, dv,
+                             bws)
         else:
             _OPS["varlen_bwd"](do, dr, q, k, v, cu_seqlens, int(max_seqlens), ws, float(logit_scale), bool(attend_current),
-                               dq, dk, dv, bws)
+                               bool(fused), rem, dq, dk, dv, bws)
     else:
         _backward_into(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale, attend_current, phases, dq, dk,
-                       dv, bws)
+                       dv, bws, fused, rem)
     return dq, dk, dv
 
 
-def varlen_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=False, no_grad=False):
+def fusable(q):
+    """Whether the fused remainder (out = o + rem * v inside the kernels) is available for tensors like q: it exists in
+    the tensor-core kernels only."""
+    return (q.dtype in (torch.bfloat16, torch.float16) and q.size(-1) in (64, 128) and _forced_path != "simt"
+            and q.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in q.stride()[:-1]))
+
+
+def varlen_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=False, no_grad=False, fuse_remainder=False):
     """Packed layout: q, k, v [H, T, D]; cu_seqlens = cumulative sequence ends without a leading zero.
 
     Returns (o, rem, neg_log_acc, workspace).  Mirrors varlen_fwd of the reference (sb_varlen_fwd.py:411-452)."""
     _check_qkv(q, k, v, 3)
     cu_seqlens, max_seqlens = _prep_cu(cu_seqlens, q, max_seqlens)
-    return _forward(q, k, v, False, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad)
+    return _forward(q, k, v, False, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, fuse_remainder)
 
 
 def varlen_bwd(do, dr, q, k, v, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current=False, phases=0,
-               out=None, bwd_workspace=None):
+               out=None, bwd_workspace=None, fuse_remainder=False, rem=None):
     """Returns (dq, dk, dv).  Mirrors varlen_bwd of the reference (sb_varlen_bwd.py:483-539); ``workspace`` takes
     the place of its ``neg_log_acc`` argument.  ``phases`` (1: dq kernel only, 2: dk/dv kernel only), ``out`` and
     ``bwd_workspace`` exist for benchmarking the two backward kernels apart; leave them at their defaults."""
     _check_qkv(q, k, v, 3)
     cu_seqlens, max_seqlens = _prep_cu(cu_seqlens, q, max_seqlens)
     return _backward(do, dr, q, k, v, False, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current, phases,
-                     out, bwd_workspace)
+                     out, bwd_workspace, fuse_remainder, rem)
 
 
-def attn_fwd(q, k, v, logit_scale, attend_current=False, no_grad=False):
+def attn_fwd(q, k, v, logit_scale, attend_current=False, no_grad=False, fuse_remainder=False):
     """Batched layout: q, k, v [B, H, T, D].  Mirrors _fwd of the reference (sb_attn/sb_fwd.py:137-173)."""
     _check_qkv(q, k, v, 4)
-    return _forward(q, k, v, True, None, q.size(2), logit_scale, attend_current, no_grad)
+    return _forward(q, k, v, True, None, q.size(2), logit_scale, attend_current, no_grad, fuse_remainder)
 
 
-def attn_bwd(do, dr, q, k, v, workspace, logit_scale, attend_current=False):
+def attn_bwd(do, dr, q, k, v, workspace, logit_scale, attend_current=False, fuse_remainder=False, rem=None):
     """Mirrors _bwd of the reference (sb_attn/sb_bwd.py:162-204)."""
     _check_qkv(q, k, v, 4)
-    return _backward(do, dr, q, k, v, True, None, q.size(2), workspace, logit_scale, attend_current)
+    return _backward(do, dr, q, k, v, True, None, q.size(2), workspace, logit_scale, attend_current, 0, None, None,
+                     fuse_remainder, rem)
