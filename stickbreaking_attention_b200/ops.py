@@ -318,8 +318,11 @@ def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale
 def fusable(q):
     """Whether the fused remainder (out = o + rem * v inside the kernels) is available for tensors like q: it exists in
     the tensor-core kernels only."""
-    return (q.dtype in (torch.bfloat16, torch.float16) and q.size(-1) in (64, 128) and _forced_path != "simt"
-            and q.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in q.stride()[:-1]))
+    if not (q.dtype in (torch.bfloat16, torch.float16) and q.size(-1) in (64, 128) and _forced_path != "simt"
+            and all(st % 8 == 0 for st in q.stride()[:-1])):
+        return False
+    # addresses are not visible while a program is being traced: a misaligned tensor then fails in the operator
+    return torch.compiler.is_compiling() or q.data_ptr() % 16 == 0
 
 
 def varlen_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=False, no_grad=False, fuse_remainder=False):

@@ -46,3 +46,19 @@ def test_batched_compiled_matches_eager():
     compiled = _grads(torch.compile(fn, backend="aot_eager", fullgraph=True), q, k, v, do, dr)
     for a, b in zip(eager, compiled):
         assert torch.equal(a, b)
+
+
+def test_fused_remainder_compiled_matches_eager():
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    lengths = [200, 130, 182]
+    H, T, D = 2, sum(lengths), 128
+    q, k, v, do, dr = (torch.from_numpy(x).to("cuda", torch.bfloat16) for x in synth(H, T, D, 6))
+    cu = torch.tensor(np.cumsum(lengths), dtype=torch.int32, device="cuda")
+
+    def fn(q, k, v):
+        return sb_attn_varlen(q, k, v, cu, max(lengths), zero_start=False, fuse_remainder=True)
+
+    eager = _grads(fn, q, k, v, do, dr)
+    compiled = _grads(torch.compile(fn, backend="aot_eager", fullgraph=True), q, k, v, do, dr)
+    for a, b in zip(eager, compiled):
+        assert torch.equal(a, b)
