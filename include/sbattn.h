@@ -143,6 +143,17 @@ int sbattn_fwd_static(const SbParams* p);
 /* Size in bytes of the built-in scratch of sbattn_fwd_static.  No counterpart in the reference. */
 size_t sbattn_static_scratch_bytes(void);
 
+/* Attention weights as a dense float32 matrix, a debugging aid: w[b][h][i][j] = weight of key j in the output of
+ * query i, written for every visible pair (j < i, or j <= i with attend_current); the other entries keep what the
+ * caller put there (the reference fills the matrix with zeros first).  Replaces the return_attention=True mode of
+ * varlen_fwd (sb_varlen_fwd.py:194-201, W allocated at :420-422 as [H,T,T]) and of _fwd (sb_fwd.py:145-147,
+ * [B,H,T,T]).  Uses dtype, batch, heads, tokens, head_dim, num_seqs, cu_width, cu_seqlens, attend_current, inv_temp,
+ * q, k and stream of p; no workspace.  Strides in elements; the column stride is 1 and stride_m >= tokens.
+ * Packed layout: i and j are token indices of the pack, so each sequence fills its own diagonal block.  (The reference
+ * offsets a sequence's block by its start along the columns only, sb_varlen_fwd.py:316; both agree for a pack of
+ * one sequence.)  Float32 arithmetic whatever the dtype; cost O(T^2 D) per head with no tensor cores. */
+int sbattn_attention_weights(const SbParams* p, float* w, int64_t stride_b, int64_t stride_h, int64_t stride_m);
+
 /* Text for a return code.  No counterpart in the reference (it raises Python exceptions). */
 const char* sbattn_strerror(int code);
 

@@ -39,7 +39,7 @@ class SbParams(ctypes.Structure):
 FLAG_FUSED_REMAINDER = 1
 
 EXPORTS = ("sbattn_workspace_bytes", "sbattn_fwd", "sbattn_bwd", "sbattn_strerror", "sbattn_version",
-           "sbattn_params_size", "sbattn_fwd_static", "sbattn_static_scratch_bytes")
+           "sbattn_params_size", "sbattn_fwd_static", "sbattn_static_scratch_bytes", "sbattn_attention_weights")
 
 _lib = None
 
@@ -74,6 +74,9 @@ def lib():
         L.sbattn_fwd_static.argtypes = [ctypes.POINTER(SbParams)]
         L.sbattn_fwd_static.restype = ctypes.c_int
         L.sbattn_static_scratch_bytes.restype = ctypes.c_size_t
+        L.sbattn_attention_weights.argtypes = [ctypes.POINTER(SbParams), ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                               ctypes.c_int64]
+        L.sbattn_attention_weights.restype = ctypes.c_int
         if L.sbattn_params_size() != ctypes.sizeof(SbParams):
             raise RuntimeError("libsbattn.so and its Python binding disagree about SbParams")
         _lib = L

@@ -10,7 +10,7 @@ LIB = os.path.join(HERE, "libsbattn.so")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
          "-Xcompiler", "-fPIC"]
 # files that must keep IEEE division/exp (the float32-arithmetic kernels): compiled without --use_fast_math
-PRECISE = {"sb_simt.cu"}
+PRECISE = {"sb_simt.cu", "sb_weights.cu"}
 
 
 def sources():

@@ -158,3 +158,14 @@ extern "C" int sbattn_bwd(const SbParams* p) {
     const int e = path == 1 ? launch_tensor_bwd(*p, L, a, st) : launch_simt_bwd(*p, L, a, st);
     return e == 0 ? SBATTN_OK : SBATTN_ECUDA;
 }
+
+extern "C" int sbattn_attention_weights(const SbParams* p, float* w, int64_t stride_b, int64_t stride_h, int64_t stride_m) {
+    int rc = check_shape(p);
+    if (rc != SBATTN_OK) return rc;
+    if (empty_problem(p)) return SBATTN_OK;
+    if ((rc = check_mat(p->q, true)) || (rc = check_mat(p->k, true))) return rc;
+    if (!w) return SBATTN_ENULL;
+    if (p->batch == 0 && !p->cu_seqlens) return SBATTN_ENULL;
+    if (stride_b < 0 || stride_h < 0 || stride_m < p->tokens) return SBATTN_EINVAL;
+    return launch_weights(*p, w, stride_b, stride_h, stride_m, (cudaStream_t)p->stream) == 0 ? SBATTN_OK : SBATTN_ECUDA;
+}

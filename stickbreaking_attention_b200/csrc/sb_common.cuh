@@ -139,5 +139,6 @@ int launch_simt_bwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaSt
 bool tensor_path_eligible(const SbParams& p, bool backward, int* why);
 int launch_tensor_fwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
 int launch_tensor_bwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
+int launch_weights(const SbParams& p, float* w, int64_t stride_b, int64_t stride_h, int64_t stride_m, cudaStream_t st);
 
 }  // namespace sb

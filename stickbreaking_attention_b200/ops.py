@@ -325,13 +325,41 @@ def fusable(q):
     return torch.compiler.is_compiling() or q.data_ptr() % 16 == 0
 
 
-def varlen_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=False, no_grad=False, fuse_remainder=False):
+def attention_weights(q, k, cu_seqlens=None, logit_scale=None, attend_current=False):
+    """The attention matrix in float32, for debugging: [H, T, T] for the packed layout (cu_seqlens given; row and column
+    are token indices of the pack, each sequence fills its diagonal block), [B, H, T, T] for the batched one.  Entries of
+    pairs that are not attended are zero.  What the reference's launchers return as ``W`` with return_attention=True
+    (sb_varlen_fwd.py:420-422,447-448; sb_fwd.py:145-147,169-170)."""
+    batched = cu_seqlens is None
+    _check_qkv(q, k, k, 4 if batched else 3)
+    _require_cuda(q, k)
+    q, k = _unit_inner(q), _unit_inner(k)
+    if logit_scale is None:
+        logit_scale = q.size(-1) ** -0.5
+    if not batched:
+        cu_seqlens, _ = _prep_cu(cu_seqlens, q, q.size(1))
+    tokens = q.size(-2)
+    w = torch.zeros(q.shape[:-1] + (tokens,), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        p = _base_params(q, batched, cu_seqlens, tokens, logit_scale, attend_current, False)
+        p.q, p.k = _mat(q, batched), _mat(k, batched)
+        _lib.check(_lib.lib().sbattn_attention_weights(ctypes.byref(p), w.data_ptr(), w.stride(0) if batched else 0,
+                                                       w.stride(-3), w.stride(-2)), "sbattn_attention_weights")
+    return w
+
+
+def varlen_fwd(q, k, v, cu_seqlens, max_seqlens, logit_scale, attend_current=False, no_grad=False, fuse_remainder=False,
+               return_attention=False):
     """Packed layout: q, k, v [H, T, D]; cu_seqlens = cumulative sequence ends without a leading zero.
 
-    Returns (o, rem, neg_log_acc, workspace).  Mirrors varlen_fwd of the reference (sb_varlen_fwd.py:411-452)."""
+    Returns (o, rem, neg_log_acc, workspace) and, with ``return_attention``, the float32 attention matrix [H, T, T] after
+    them.  Mirrors varlen_fwd of the reference (sb_varlen_fwd.py:411-452)."""
     _check_qkv(q, k, v, 3)
     cu_seqlens, max_seqlens = _prep_cu(cu_seqlens, q, max_seqlens)
-    return _forward(q, k, v, False, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, fuse_remainder)
+    out = _forward(q, k, v, False, cu_seqlens, max_seqlens, logit_scale, attend_current, no_grad, fuse_remainder)
+    if return_attention:
+        return out + (attention_weights(q, k, cu_seqlens, logit_scale, attend_current),)
+    return out
 
 
 def varlen_bwd(do, dr, q, k, v, cu_seqlens, max_seqlens, workspace, logit_scale, attend_current=False, phases=0,
@@ -345,10 +373,14 @@ def varlen_bwd(do, dr, q, k, v, cu_seqlens, max_seqlens, workspace, logit_scale,
                      out, bwd_workspace, fuse_remainder, rem)
 
 
-def attn_fwd(q, k, v, logit_scale, attend_current=False, no_grad=False, fuse_remainder=False):
-    """Batched layout: q, k, v [B, H, T, D].  Mirrors _fwd of the reference (sb_attn/sb_fwd.py:137-173)."""
+def attn_fwd(q, k, v, logit_scale, attend_current=False, no_grad=False, fuse_remainder=False, return_attention=False):
+    """Batched layout: q, k, v [B, H, T, D].  Mirrors _fwd of the reference (sb_attn/sb_fwd.py:137-173); with
+    ``return_attention`` the float32 attention matrix [B, H, T, T] follows the other results."""
     _check_qkv(q, k, v, 4)
-    return _forward(q, k, v, True, None, q.size(2), logit_scale, attend_current, no_grad, fuse_remainder)
+    out = _forward(q, k, v, True, None, q.size(2), logit_scale, attend_current, no_grad, fuse_remainder)
+    if return_attention:
+        return out + (attention_weights(q, k, None, logit_scale, attend_current),)
+    return out
 
 
 def attn_bwd(do, dr, q, k, v, workspace, logit_scale, attend_current=False, fuse_remainder=False, rem=None):

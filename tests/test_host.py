@@ -56,6 +56,10 @@ def test_argument_errors_without_gpu(lib):
     assert lib.sbattn_fwd(ctypes.byref(params())) == -2          # null q
     assert lib.sbattn_bwd(ctypes.byref(params())) == -2
     assert lib.sbattn_fwd(ctypes.byref(params(heads=0))) == 0    # empty problem: nothing to do
+    lib.sbattn_attention_weights.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64]
+    assert lib.sbattn_attention_weights(None, None, 0, 0, 0) == -2
+    assert lib.sbattn_attention_weights(ctypes.byref(params()), None, 0, 0, 1024) == -2   # null q
+    assert lib.sbattn_attention_weights(ctypes.byref(params(heads=0)), None, 0, 0, 0) == 0
     for code in range(0, -7, -1):
         assert lib.sbattn_strerror(code)
 
