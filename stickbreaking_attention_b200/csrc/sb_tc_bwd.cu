@@ -73,8 +73,10 @@ __device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, f
 constexpr int kDqThreads = 352;
 constexpr int kDqKStages = 3, kDqVStages = 2;
 enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_FULL2, A_K_EMPTY0, A_K_EMPTY1, A_K_EMPTY2, A_V_FULL0, A_V_FULL1,
-             A_V_EMPTY0, A_V_EMPTY1, A_S_READY0, A_S_READY1, A_DP_READY, A_LOADED, A_DS_READY, A_X_G0, A_X_G1, A_X_G2, A_X_G3, A_DQ_READY,
-             A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1, kNumDqBars };
+             A_V_EMPTY0, A_V_EMPTY1, A_S_READY0, A_S_READY1, A_DP_READY, A_LOADED, A_DS_READY, A_DQ_READY,
+             A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1,
+             A_X_G0,  // 16 barriers: [group][step parity][warp of the group]
+             kNumDqBars = A_X_G0 + 16 };
 
 template <bool kMasked>
 __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[32], float scale, int col0, int lim,
@@ -150,7 +152,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (tid == 0) {
         for (int i = 0; i < kNumDqBars; ++i) {
             uint32_t cnt = 1;
-            if (i >= A_X_G0 && i <= A_X_G3) cnt = 128;
+            if (i >= A_X_G0) cnt = 32;
             if (i == A_LOADED || i == A_DS_READY || i == A_DQ_FREE) cnt = 256;
             if (i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) cnt = 258;  // MMA warp (one lane), V producer, 256 row threads
             mbar_init(&bars[i], cnt);
@@ -395,13 +397,14 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 dq_half_local(sr, gr, cl);
                 if (r == 0) SB_TRACE_EV(c, 1 + grp, 3);
                 // The two threads of a row exchange the totals of their halves.  Every thread has begun this step (and so
-                // has read the previous step's total) once it has arrived at A_LOADED; two barriers per group, by step
-                // parity, so that a waiter is never two phases away from the phase it names.
+                // has read the previous step's total) once it has arrived at A_LOADED.  One barrier per warp (a warp waits
+                // for the warp that holds the other halves of its rows, not for the whole group) and step parity, so that
+                // a waiter is never two phases away from the phase it names.
                 ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
                 if (!ok) break;
                 xg[grp * 128 + r] = cl;
-                mbar_arrive(&bars[A_X_G0 + 2 * grp + (g & 1)]);
-                ok = mbar_wait(&bars[A_X_G0 + 2 * (grp ^ 1) + (g & 1)], (g >> 1) & 1, abort_flag);
+                mbar_arrive(&bars[A_X_G0 + 8 * grp + 4 * (g & 1) + (warp & 3)]);
+                ok = mbar_wait(&bars[A_X_G0 + 8 * (grp ^ 1) + 4 * (g & 1) + (warp & 3)], (g >> 1) & 1, abort_flag);
                 if (!ok) break;
                 const float other = xg[(grp ^ 1) * 128 + r];
                 const float c_edge = hf ? c_in + other : c_in;  // prefix at the left edge of this half

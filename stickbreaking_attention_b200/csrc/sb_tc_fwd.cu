@@ -36,7 +36,9 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColO = 384, kColPOff = 64;  // S buffer i at 128*i (i = step mod 3), its P at +64
 constexpr int kKStages = 3, kVStages = 2;
 enum FwdBar { Q_FULL, Q_EMPTY, K_FULL0, K_FULL1, K_FULL2, K_EMPTY0, K_EMPTY1, K_EMPTY2, V_FULL0, V_FULL1, V_EMPTY0, V_EMPTY1, S_READY0, S_READY1,
-              S_READY2, P_READY0, P_READY1, P_READY2, X_W0, X_W1, O_READY, O_FREE, WORK_FULL0, WORK_FULL1, WORK_EMPTY0, WORK_EMPTY1, kNumBars };
+              S_READY2, P_READY0, P_READY1, P_READY2, O_READY, O_FREE, WORK_FULL0, WORK_FULL1, WORK_EMPTY0, WORK_EMPTY1,
+              X_W0,  // 8 barriers: [group][warp of the group]
+              kNumBars = X_W0 + 8 };
 
 // With e = exp(s) and d = 1 + e:  beta = e / d,  1 - beta = 1 / d.  For key m of a group of 8 keys entered with the
 // carry W (product of 1 - beta over everything to its right)
@@ -108,7 +110,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i) {
             uint32_t cnt = 1;
-            if (i == P_READY0 || i == P_READY1 || i == P_READY2 || i == X_W0 || i == X_W1) cnt = 128;
+            if (i == P_READY0 || i == P_READY1 || i == P_READY2) cnt = 128;
+            if (i >= X_W0) cnt = 32;  // a warp waits for the warp that holds the same rows in the other group
             if (i == O_FREE) cnt = 256;
             if (i == WORK_EMPTY0 || i == WORK_EMPTY1) cnt = 258;  // MMA thread, V producer, 256 row threads
             mbar_init(&bars[i], cnt);
@@ -329,7 +332,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 // the true entering carry comes from the partner thread, which swept the tile to the right
                 float Win = 1.f;
                 if (j > 0) {
-                    ok = mbar_wait(&bars[X_W0 + (b ^ 1)], ph_x, abort_flag);
+                    ok = mbar_wait(&bars[X_W0 + 4 * (b ^ 1) + (warp & 3)], ph_x, abort_flag);
                     ph_x ^= 1;
                     if (!ok) break;
                     Win = x_other[r];
@@ -337,7 +340,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 W = Win * Wl;
                 if (j + 1 < n) {
                     x_mine[r] = W;
-                    mbar_arrive(&bars[X_W0 + b]);
+                    mbar_arrive(&bars[X_W0 + 4 * b + (warp & 3)]);
                 } else if (kFused) {
                     wfin[(items & 1) * 128 + r] = W;  // visible to both groups once O_READY has completed
                 }
