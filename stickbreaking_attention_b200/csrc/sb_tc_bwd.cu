@@ -58,25 +58,35 @@ __device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, f
 }
 
 // ================================================================================================ dq kernel
-// One block per SM (352 threads), one work item = (head, sequence, 128-row query tile) at a time, walked LEFT TO RIGHT in
-// steps of 128 keys, so that every contraction runs at the widest shape: S and dP [128 q x 128 keys], dQ += dS K with
-// K = 128 (an MMA instruction costs the same for N = 64 and N = 128; 64-key steps need 40 instructions per 128 x 128
-// scores, 128-key steps 24).  Warps 0-3 own the right 64 keys of a step, warps 4-7 the left 64 keys, one thread per
-// query row in each; the halves are entered independently with the forward's carry (carry_w exists at every 64-key
-// boundary).  The prefix of g that ds needs is local to a half up to a constant: a thread computes
-// a = g - beta * (prefix inside its half), the two threads of a row exchange the totals of their halves through shared
-// memory, and ds = a - beta * (prefix at the half's left edge).
+// One block per SM (608 threads, at most 104 registers each), one work item = (head, sequence, 128-row query tile) at a
+// time, walked LEFT TO RIGHT in steps of 128 keys, so that every contraction runs at the widest shape: S and dP
+// [128 q x 128 keys], dQ += dS K with K = 128 (an MMA instruction costs the same for N = 64 and N = 128; 64-key steps need
+// 40 instructions per 128 x 128 scores, 128-key steps 24).
+// Sixteen row warps: a thread owns one query row and a quarter (32 keys) of the step, warps 0-3 the rightmost quarter ...
+// warps 12-15 the leftmost, so that every scheduler has four row warps to choose from (with eight row warps of 64 keys
+// per thread the same arithmetic ran 20 % slower, and all of them waited at the same time).
+//   * carry_w exists at every 64-key boundary: the right quarter of a half enters with it; the left quarter sweeps
+//     relative to a carry of 1 and receives the true carry (what the right quarter is left with) before its results are
+//     used: g, a and the quarter's total are linear in it.
+//   * The prefix of g that ds needs is local to a quarter up to a constant: a thread computes
+//     a = g - beta * (prefix inside its quarter) and ds = a - beta * (prefix at the quarter's left edge).  That prefix
+//     travels along the row as a chain through shared memory: a thread takes it from the quarter to its left (the leftmost
+//     quarter from the rightmost one of the previous step), adds its total and passes it on.  Nobody waits for a quarter
+//     to its right, so the quarters settle into a stagger and the waits of one overlap with the arithmetic of another.
+//   * One exchange slot per quarter and row: the right quarter of a half puts the carry into its left neighbour's slot,
+//     which that thread reads and then overwrites with its prefix; the only reader of that prefix is the right quarter
+//     again.
 // Tensor memory: S in two buffers (S of the next step is computed while this one is worked on; dS overwrites the left
 // half of its S buffer as 16-bit operands), dP in one (released as soon as every thread has copied its values to
-// registers), dQ.  Warp 8 loads Q, dO (once per item) and the K tiles (three-stage ring: a K tile is needed for S early
-// and for dQ late), warp 10 the V tiles, warp 9 issues every tcgen05.mma.
-constexpr int kDqThreads = 352;
+// registers), dQ.  Warp 16 loads Q, dO (once per item) and the K tiles (three-stage ring: a K tile is needed for S early
+// and for dQ late), warp 18 the V tiles, warp 17 issues every tcgen05.mma.
+constexpr int kDqThreads = 608;
 constexpr int kDqKStages = 3, kDqVStages = 2;
 enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_FULL2, A_K_EMPTY0, A_K_EMPTY1, A_K_EMPTY2, A_V_FULL0, A_V_FULL1,
              A_V_EMPTY0, A_V_EMPTY1, A_S_READY0, A_S_READY1, A_DP_READY, A_LOADED, A_DS_READY, A_DQ_READY,
              A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1,
-             A_X_G0,  // 16 barriers: [group][step parity][warp of the group]
-             kNumDqBars = A_X_G0 + 16 };
+             A_X_G0,  // 32 barriers for the prefixes [quarter][step parity][warp & 3], 16 for the carries [half][step parity][warp & 3]
+             kNumDqBars = A_X_G0 + 48 };
 
 template <bool kMasked>
 __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[32], float scale, int col0, int lim,
@@ -104,7 +114,7 @@ __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[
         }
     }
 }
-// left to right: g <- a = g - beta * (inclusive prefix of g inside the half); c carries the running prefix
+// left to right: g <- a = g - beta * (inclusive prefix of g inside the 32 columns); c carries the running prefix
 __device__ __forceinline__ void dq_half_local(const uint32_t (&beta)[32], uint32_t (&g)[32], float& c) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -124,6 +134,18 @@ __device__ __forceinline__ void dq_half_finish(const uint32_t (&beta)[32], const
     }
 }
 
+// the same for a quarter that swept relative to a carry of 1: a is scaled by the true carry first
+template <bool kF16>
+__device__ __forceinline__ void dq_half_finish_scaled(const uint32_t (&beta)[32], const uint32_t (&av)[32], float c_in, float mul,
+                                                      uint32_t (&packed)[16]) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float2 am = __fmul2_rn(make_float2(__uint_as_float(av[2 * j]), __uint_as_float(av[2 * j + 1])), make_float2(mul, mul));
+        const float2 ds = __ffma2_rn(make_float2(__uint_as_float(beta[2 * j]), __uint_as_float(beta[2 * j + 1])),
+                                     make_float2(-c_in, -c_in), am);
+        packed[j] = pack16<kF16>(ds.x, ds.y);
+    }
+}
 // kFused (both backward kernels): d_o is the gradient of out = o + rem * v; separate instantiations, the plain ones stay
 // as they are
 template <int D, bool kF16, bool kFused>
@@ -144,27 +166,26 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumDqBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     SchedRing<Work>* ring = (SchedRing<Work>*)(tmem_slot + 2);
-    float* xg = (float*)(tmem_slot + 32);  // [group][128 rows]: total of g over the group's half of the step
-    float* wpre = xg + 256;                // [group][128 rows]: carry_w of a group's next step, copied asynchronously
+    float* xg = (float*)(tmem_slot + 32);  // [quarter][128 rows]: the exchange slots of the row threads
     static_assert(sizeof(SchedRing<Work>) <= 120, "ring does not fit its place");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < kNumDqBars; ++i) {
             uint32_t cnt = 1;
-            if (i >= A_X_G0) cnt = 32;
-            if (i == A_LOADED || i == A_DS_READY || i == A_DQ_FREE) cnt = 256;
-            if (i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) cnt = 258;  // MMA warp (one lane), V producer, 256 row threads
+            if (i >= A_X_G0) cnt = 32;  // prefixes [quarter][step parity][warp & 3], then carries [half][step parity][warp & 3]
+            if (i == A_LOADED || i == A_DS_READY || i == A_DQ_FREE) cnt = 512;
+            if (i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) cnt = 514;  // MMA warp (one lane), V producer, 512 row threads
             mbar_init(&bars[i], cnt);
         }
         *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
         fence_barrier_init();
     }
-    if (warp == 9) {
+    if (warp == 17) {
         tmem_alloc(tmem_slot, kCols);
         tmem_relinquish();
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == 16 && lane == 0) {
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
@@ -179,7 +200,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // G counts 128-key steps over all items of this block: step G uses K stage G % 3, V stage G % 2 and S buffer G % 2;
     // a barrier that completes once per use is in phase (use count) & 1.
 
-    if (warp == 8) {
+    if (warp == 16) {
         // ------------------------------------------------------------------ TMA: Q, dO per item, K ring
         if (lane == 0) {
             uint32_t G = 0, items = 0;
@@ -209,7 +230,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 18) {
         // ------------------------------------------------------------------ TMA: V ring
         if (lane == 0) {
             uint32_t G = 0;
@@ -229,7 +250,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == 17) {
         // ------------------------------------------------------------------ MMA issuer
         {
             const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
@@ -315,9 +336,9 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
         }
     } else {
-        // ------------------------------------------------------------------ row threads: group 0 right half, group 1 left half
-        const int grp = warp >> 2;
-        const int hf = grp ^ 1;  // 64-key half of the step this thread owns
+        // ------------------------------------------------------------------ row threads: warps 0-3 rightmost quarter ... 12-15 leftmost
+        const int kq = 3 - (warp >> 2);        // 32-key quarter of the step this thread owns
+        const int hf = kq >> 1, sub = kq & 1;  // its 64-key half; sub 1: right quarter of the half, enters with carry_w
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const float scale = a.inv_temp * kLog2e;
@@ -342,7 +363,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const char* dorow = a.d_o.ptr + 2 * ((int64_t)wk.b * a.d_o.sb + (int64_t)wk.h * a.d_o.sh + tok * a.d_o.st);
                 const char* vrow = a.v.ptr + 2 * ((int64_t)wk.b * a.v.sb + (int64_t)wk.h * a.v.sh + tok * a.v.st);
                 float dot = 0.f;
-#pragma unroll
+#pragma unroll 1
                 for (int cidx = 0; cidx < D / 32; ++cidx) {
                     float x[32], y[32];
                     load_row32<kF16>(dorow + cidx * 64, x);
@@ -351,89 +372,92 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     for (int i = 0; i < 32; ++i) dot = fmaf(x[i], y[i], dot);
                 }
                 drem += dot;
-                if (grp == 0) a.drem_eff[(int64_t)wk.h * a.drem_rows + (int64_t)wk.b * a.tokens + wk.start + qi] = drem;
+                if (kq == 3) a.drem_eff[(int64_t)wk.h * a.drem_rows + (int64_t)wk.b * a.tokens + wk.start + qi] = drem;
             }
             const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
-            // the carry of a step is copied to shared memory one step ahead (cp.async): held in a register it would be
-            // spilled, and the spill store would wait for the load
-            float* wslot = wpre + grp * 128 + r;
             // the half may lie beyond the end of the sequence (its carry slot does not exist): then W = 0, no weights
             const auto half_ok = [&](int j) { return row_ok && (2 * j + hf) * kBK < wk.len; };
-            if (half_ok(0)) cp_async4(wslot, cw + carry_slot(wk.slot_base, wk.qt, hf) * kTileQ);
-            float c_in = 0.f;  // prefix of g at the left edge of the step
             for (int j = 0; j < n; ++j) {
                 const uint32_t g = G + j, buf = g & 1;
                 const int kh = 2 * j + hf;
                 const int64_t slot = carry_slot(wk.slot_base, wk.qt, kh) * kTileQ;
-                cp_async_wait_all();
-                float W = half_ok(j) ? *wslot : 0.f;
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 1);
+                float W = 1.f;
+                if (sub) W = half_ok(j) ? __ldg(cw + slot) : 0.f;
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 1);
                 ok = mbar_wait(&bars[A_S_READY0 + buf], (g >> 1) & 1, abort_flag) && mbar_wait(&bars[A_DP_READY], g & 1, abort_flag);
                 if (!ok) break;
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 2);
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 2);
                 tc_fence_after();
                 const bool masked = kh >= 2 * wk.qt;  // the half reaches the diagonal
                 const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
-                uint32_t sr[32], gr[32], sl[32], gl[32], packed[16];
-                tmem_ld32(lane_base + kColS + 128 * buf + 64 * hf + 32, sr);
-                tmem_ld32(lane_base + kColDP + 64 * hf + 32, gr);
-                tmem_ld32(lane_base + kColS + 128 * buf + 64 * hf, sl);
-                tmem_ld32(lane_base + kColDP + 64 * hf, gl);
+                uint32_t sv[32], gv[32], packed[16];
+                tmem_ld32(lane_base + kColS + 128 * buf + 32 * kq, sv);
+                tmem_ld32(lane_base + kColDP + 32 * kq, gv);
                 tmem_wait_ld();
                 tc_fence_before();
                 mbar_arrive(&bars[A_LOADED]);  // dP is free; so are the S columns that dS will overwrite, once all have arrived
-                // next step's carry into the slot read above (the read is long complete: W has been used)
-                if (j + 1 < n && half_ok(j + 1)) cp_async4(wslot, cw + slot + 2 * kTileQ);
-                if (masked) {
-                    dq_half_pass1<true>(sr, gr, scale, 32, lim, drem, W);
-                    dq_half_pass1<true>(sl, gl, scale, 0, lim, drem, W);
-                } else {
-                    dq_half_pass1<false>(sr, gr, scale, 32, lim, drem, W);
-                    dq_half_pass1<false>(sl, gl, scale, 0, lim, drem, W);
-                }
-                float cl = 0.f;  // prefix of g inside the half
-                dq_half_local(sl, gl, cl);
-                dq_half_local(sr, gr, cl);
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 3);
-                // The two threads of a row exchange the totals of their halves.  Every thread has begun this step (and so
-                // has read the previous step's total) once it has arrived at A_LOADED.  One barrier per warp (a warp waits
-                // for the warp that holds the other halves of its rows, not for the whole group) and step parity, so that
-                // a waiter is never two phases away from the phase it names.
+                if (masked) dq_half_pass1<true>(sv, gv, scale, 32 * sub, lim, drem, W);
+                else dq_half_pass1<false>(sv, gv, scale, 32 * sub, lim, drem, W);
+                float cl = 0.f;  // prefix of g inside the quarter
+                dq_half_local(sv, gv, cl);
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 3);
+                // Every thread has begun this step (and so has read the previous step's slots) once it has arrived at
+                // A_LOADED.  Barriers by step parity, so that a waiter is never two phases away from the phase it names.
                 ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
                 if (!ok) break;
-                xg[grp * 128 + r] = cl;
-                mbar_arrive(&bars[A_X_G0 + 8 * grp + 4 * (g & 1) + (warp & 3)]);
-                ok = mbar_wait(&bars[A_X_G0 + 8 * (grp ^ 1) + 4 * (g & 1) + (warp & 3)], (g >> 1) & 1, abort_flag);
-                if (!ok) break;
-                const float other = xg[(grp ^ 1) * 128 + r];
-                const float c_edge = hf ? c_in + other : c_in;  // prefix at the left edge of this half
-                if (half_ok(j)) cc[slot] = c_edge + cl;         // prefix through its right edge, for the dk/dv kernel
-                c_in += cl + other;
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 4);
+                const uint32_t par = g & 1, ph = (g >> 1) & 1;
+                uint64_t* bar_w = &bars[A_X_G0 + 32 + 8 * hf + 4 * par + (warp & 3)];
+                float mul = 1.f;
+                if (sub) {  // what is left of the carry enters the quarter to the left
+                    xg[(kq - 1) * 128 + r] = W;
+                    mbar_arrive(bar_w);
+                } else {
+                    ok = mbar_wait(bar_w, ph, abort_flag);
+                    if (!ok) break;
+                    mul = xg[kq * 128 + r];
+                    cl *= mul;
+                }
+                // The prefix of g travels along the row as a chain: a thread takes the prefix at its left edge from the
+                // quarter to its left (the leftmost one from the rightmost quarter of the previous step), adds its total
+                // and passes it on.  Nobody waits for a quarter to its right, so the quarters settle into a stagger and
+                // the waits of one overlap with the arithmetic of another.
+                float c_edge = 0.f;
+                if (kq > 0) {
+                    ok = mbar_wait(&bars[A_X_G0 + 8 * (kq - 1) + 4 * par + (warp & 3)], ph, abort_flag);
+                    if (!ok) break;
+                    c_edge = xg[(kq - 1) * 128 + r];
+                } else if (j > 0) {
+                    ok = mbar_wait(&bars[A_X_G0 + 8 * 3 + 4 * (par ^ 1) + (warp & 3)], ((g - 1) >> 1) & 1, abort_flag);
+                    if (!ok) break;
+                    c_edge = xg[3 * 128 + r];
+                }
+                const float c_right = c_edge + cl;  // prefix through the quarter's right edge
+                xg[kq * 128 + r] = c_right;
+                mbar_arrive(&bars[A_X_G0 + 8 * kq + 4 * par + (warp & 3)]);
+                if (sub && half_ok(j)) cc[slot] = c_right;  // through the right edge of the half, for the dk/dv kernel
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 4);
                 // dS goes to columns [0, 64) of the S buffer: every thread has read its scores (A_LOADED, above)
-                dq_half_finish<kF16>(sl, gl, c_edge, packed);
-                tmem_st16(lane_base + kColS + 128 * buf + 32 * hf, packed);
-                dq_half_finish<kF16>(sr, gr, c_edge, packed);
-                tmem_st16(lane_base + kColS + 128 * buf + 32 * hf + 16, packed);
+                if (sub) dq_half_finish<kF16>(sv, gv, c_edge, packed);
+                else dq_half_finish_scaled<kF16>(sv, gv, c_edge, mul, packed);
+                tmem_st16(lane_base + kColS + 128 * buf + 16 * kq, packed);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars[A_DS_READY]);
-                if (r == 0) SB_TRACE_EV(c, 1 + grp, 5);
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 5);
             }
             if (!ok) break;
-            // epilogue: each group stores half of the head dim of every row
+            // epilogue: the quarters store 32 columns of every row each
             ok = mbar_wait(&bars[A_DQ_READY], items & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const int d0 = grp * (D / 2);
-            char* orow = a.dq.ptr + 2 * ((int64_t)wk.b * a.dq.sb + (int64_t)wk.h * a.dq.sh + tok * a.dq.st + d0);
-#pragma unroll
-            for (int cidx = 0; cidx < D / 64; ++cidx) {
+            if (kq < D / 32) {
+                const int d0 = kq * 32;
+                char* orow = a.dq.ptr + 2 * ((int64_t)wk.b * a.dq.sb + (int64_t)wk.h * a.dq.sh + tok * a.dq.st + d0);
                 uint32_t v[32];
-                tmem_ld32(lane_base + kColDQ + d0 + cidx * 32, v);
+                tmem_ld32(lane_base + kColDQ + d0, v);
                 tmem_wait_ld();
-                if (row_ok) store_row32<kF16>(orow + cidx * 64, v, a.inv_temp);
+                if (row_ok) store_row32<kF16>(orow, v, a.inv_temp);
             }
             tc_fence_before();
             mbar_arrive(&bars[A_DQ_FREE]);
@@ -441,7 +465,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             ++items;
         }
     }
-    tc_teardown(abort_flag, a.status, tmem, kCols, 9);
+    tc_teardown(abort_flag, a.status, tmem, kCols, 17);
     sched_finish(a.sched + 2);
 }
 
