@@ -50,7 +50,7 @@ KArgs make_args(const SbParams& p, const WsLayout& L) {
     a.fused = (p.flags & SBATTN_FLAG_FUSED_REMAINDER) ? 1 : 0;
     a.tokens = p.tokens;
     a.drem_rows = (int64_t)p.tokens * (p.batch > 0 ? p.batch : 1);
-    a.slot_cap = L.slot_cap;
+    a.slot_cap = 2 * L.slot_cap;  // 32-key slots
     a.heads = p.heads;
     a.head_dim = p.head_dim;
     a.attend_current = p.attend_current ? 1 : 0;

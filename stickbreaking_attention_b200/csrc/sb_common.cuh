@@ -42,7 +42,7 @@ struct WsLayout {
     int32_t n_seqs;      // sequences (packed: num_seqs, batched: B)
     int32_t n_max;       // max 128-row tiles of one sequence
     int32_t max_items;   // upper bound on items per head
-    int64_t slot_cap;    // upper bound on carry slots per head
+    int64_t slot_cap;    // upper bound on 64-key carry slots per head
     int32_t hb;          // heads (batched: heads; the batch index comes from the sequence)
     size_t off_seqs, off_items, off_bins, off_carry;
     size_t off_drem;     // inside the backward workspace
@@ -77,7 +77,7 @@ inline WsLayout make_layout(const SbParams& p) {
     L.off_bins = off;
     off = align_up(off + sizeof(int32_t) * (size_t)(2 * (L.n_max + 2)), 256);
     L.off_carry = off;
-    const size_t carry = sizeof(float) * (size_t)L.hb * (size_t)L.slot_cap * kTileQ;
+    const size_t carry = sizeof(float) * (size_t)L.hb * (size_t)(2 * L.slot_cap) * kTileQ;  // two 32-key carries per slot
     L.fwd_bytes = off + (p.save_carries ? carry : 0);
     L.off_drem = align_up(carry, 256);  // after carry_c: drem + do . v per (head, token), fused-remainder backward
     L.bwd_bytes = L.off_drem + align_up(sizeof(float) * (size_t)p.heads * (size_t)p.tokens * (size_t)(batched ? p.batch : 1), 256);
@@ -101,7 +101,7 @@ struct KArgs {
     const WsHeader* hdr;
     const SeqInfo* seqs;
     const int2* items;      // (sequence, 128-row tile), heaviest first
-    float* carry_w;         // forward carries  [heads][slot_cap][128], may be null in a no-grad forward
+    float* carry_w;         // forward carries  [heads][slot_cap][128], may be null in a no-grad forward; slot_cap: 32-key slots
     float* carry_c;         // backward carries [heads][slot_cap][128]
     int64_t slot_cap;
     int32_t heads, head_dim, attend_current;
@@ -117,9 +117,15 @@ struct KArgs {
     uint32_t* status;
 };
 
-// carry slot of (128-row tile qt of a sequence, 64-key tile kh): kh in [0, 2*qt+1]
+// Carries exist at every 32-key boundary.  carry_slot32: (128-row tile qt of a sequence, 32-key quarter kq in [0, 4*qt+3]),
+// the value at the quarter's right edge.  carry_slot: the same for the 64-key half kh in [0, 2*qt+1], i.e. its right quarter
+// (the fp32-arithmetic kernels work in 64-key halves and use these alone).  slot_base and WsLayout::slot_cap count
+// 64-key slots, KArgs::slot_cap 32-key slots.
+__host__ __device__ inline int64_t carry_slot32(int32_t slot_base, int32_t qt, int32_t kq) {
+    return 2 * ((int64_t)slot_base + (int64_t)qt * (qt + 1)) + kq;
+}
 __host__ __device__ inline int64_t carry_slot(int32_t slot_base, int32_t qt, int32_t kh) {
-    return (int64_t)slot_base + (int64_t)qt * (qt + 1) + kh;
+    return carry_slot32(slot_base, qt, 2 * kh + 1);
 }
 
 template <typename T> __device__ inline float to_f32(T x);

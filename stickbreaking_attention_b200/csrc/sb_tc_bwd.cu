@@ -65,17 +65,13 @@ __device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, f
 // Sixteen row warps: a thread owns one query row and a quarter (32 keys) of the step, warps 0-3 the rightmost quarter ...
 // warps 12-15 the leftmost, so that every scheduler has four row warps to choose from (with eight row warps of 64 keys
 // per thread the same arithmetic ran 20 % slower, and all of them waited at the same time).
-//   * carry_w exists at every 64-key boundary: the right quarter of a half enters with it; the left quarter sweeps
-//     relative to a carry of 1 and receives the true carry (what the right quarter is left with) before its results are
-//     used: g, a and the quarter's total are linear in it.
+//   * carry_w exists at every 32-key boundary: every quarter is entered independently with the forward's carry.
 //   * The prefix of g that ds needs is local to a quarter up to a constant: a thread computes
 //     a = g - beta * (prefix inside its quarter) and ds = a - beta * (prefix at the quarter's left edge).  That prefix
 //     travels along the row as a chain through shared memory: a thread takes it from the quarter to its left (the leftmost
 //     quarter from the rightmost one of the previous step), adds its total and passes it on.  Nobody waits for a quarter
 //     to its right, so the quarters settle into a stagger and the waits of one overlap with the arithmetic of another.
-//   * One exchange slot per quarter and row: the right quarter of a half puts the carry into its left neighbour's slot,
-//     which that thread reads and then overwrites with its prefix; the only reader of that prefix is the right quarter
-//     again.
+//     The prefix through a quarter's right edge is also what the dk/dv kernel enters that quarter with (carry_c).
 // Tensor memory: S in two buffers (S of the next step is computed while this one is worked on; dS overwrites the left
 // half of its S buffer as 16-bit operands), dP in one (released as soon as every thread has copied its values to
 // registers), dQ.  Warp 16 loads Q, dO (once per item) and the K tiles (three-stage ring: a K tile is needed for S early
@@ -85,8 +81,8 @@ constexpr int kDqKStages = 3, kDqVStages = 2;
 enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_FULL2, A_K_EMPTY0, A_K_EMPTY1, A_K_EMPTY2, A_V_FULL0, A_V_FULL1,
              A_V_EMPTY0, A_V_EMPTY1, A_S_READY0, A_S_READY1, A_DP_READY, A_LOADED, A_DS_READY, A_DQ_READY,
              A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1,
-             A_X_G0,  // 32 barriers for the prefixes [quarter][step parity][warp & 3], 16 for the carries [half][step parity][warp & 3]
-             kNumDqBars = A_X_G0 + 48 };
+             A_X_G0,  // 32 barriers for the prefixes: [quarter][step parity][warp & 3]
+             kNumDqBars = A_X_G0 + 32 };
 
 template <bool kMasked>
 __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[32], float scale, int col0, int lim,
@@ -134,18 +130,6 @@ __device__ __forceinline__ void dq_half_finish(const uint32_t (&beta)[32], const
     }
 }
 
-// the same for a quarter that swept relative to a carry of 1: a is scaled by the true carry first
-template <bool kF16>
-__device__ __forceinline__ void dq_half_finish_scaled(const uint32_t (&beta)[32], const uint32_t (&av)[32], float c_in, float mul,
-                                                      uint32_t (&packed)[16]) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const float2 am = __fmul2_rn(make_float2(__uint_as_float(av[2 * j]), __uint_as_float(av[2 * j + 1])), make_float2(mul, mul));
-        const float2 ds = __ffma2_rn(make_float2(__uint_as_float(beta[2 * j]), __uint_as_float(beta[2 * j + 1])),
-                                     make_float2(-c_in, -c_in), am);
-        packed[j] = pack16<kF16>(ds.x, ds.y);
-    }
-}
 // kFused (both backward kernels): d_o is the gradient of out = o + rem * v; separate instantiations, the plain ones stay
 // as they are
 template <int D, bool kF16, bool kFused>
@@ -173,7 +157,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (tid == 0) {
         for (int i = 0; i < kNumDqBars; ++i) {
             uint32_t cnt = 1;
-            if (i >= A_X_G0) cnt = 32;  // prefixes [quarter][step parity][warp & 3], then carries [half][step parity][warp & 3]
+            if (i >= A_X_G0) cnt = 32;
             if (i == A_LOADED || i == A_DS_READY || i == A_DQ_FREE) cnt = 512;
             if (i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) cnt = 514;  // MMA warp (one lane), V producer, 512 row threads
             mbar_init(&bars[i], cnt);
@@ -338,7 +322,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     } else {
         // ------------------------------------------------------------------ row threads: warps 0-3 rightmost quarter ... 12-15 leftmost
         const int kq = 3 - (warp >> 2);        // 32-key quarter of the step this thread owns
-        const int hf = kq >> 1, sub = kq & 1;  // its 64-key half; sub 1: right quarter of the half, enters with carry_w
+        const int hf = kq >> 1, sub = kq & 1;  // its 64-key half (the unit of masking) and the quarter inside it
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const float scale = a.inv_temp * kLog2e;
@@ -381,9 +365,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             for (int j = 0; j < n; ++j) {
                 const uint32_t g = G + j, buf = g & 1;
                 const int kh = 2 * j + hf;
-                const int64_t slot = carry_slot(wk.slot_base, wk.qt, kh) * kTileQ;
-                float W = 1.f;
-                if (sub) W = half_ok(j) ? __ldg(cw + slot) : 0.f;
+                const int64_t slot = carry_slot32(wk.slot_base, wk.qt, 4 * j + kq) * kTileQ;
+                float W = half_ok(j) ? __ldg(cw + slot) : 0.f;
                 if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 1);
                 ok = mbar_wait(&bars[A_S_READY0 + buf], (g >> 1) & 1, abort_flag) && mbar_wait(&bars[A_DP_READY], g & 1, abort_flag);
                 if (!ok) break;
@@ -407,17 +390,6 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
                 if (!ok) break;
                 const uint32_t par = g & 1, ph = (g >> 1) & 1;
-                uint64_t* bar_w = &bars[A_X_G0 + 32 + 8 * hf + 4 * par + (warp & 3)];
-                float mul = 1.f;
-                if (sub) {  // what is left of the carry enters the quarter to the left
-                    xg[(kq - 1) * 128 + r] = W;
-                    mbar_arrive(bar_w);
-                } else {
-                    ok = mbar_wait(bar_w, ph, abort_flag);
-                    if (!ok) break;
-                    mul = xg[kq * 128 + r];
-                    cl *= mul;
-                }
                 // The prefix of g travels along the row as a chain: a thread takes the prefix at its left edge from the
                 // quarter to its left (the leftmost one from the rightmost quarter of the previous step), adds its total
                 // and passes it on.  Nobody waits for a quarter to its right, so the quarters settle into a stagger and
@@ -435,11 +407,10 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const float c_right = c_edge + cl;  // prefix through the quarter's right edge
                 xg[kq * 128 + r] = c_right;
                 mbar_arrive(&bars[A_X_G0 + 8 * kq + 4 * par + (warp & 3)]);
-                if (sub && half_ok(j)) cc[slot] = c_right;  // through the right edge of the half, for the dk/dv kernel
+                if (half_ok(j)) cc[slot] = c_right;  // for the dk/dv kernel
                 if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 4);
                 // dS goes to columns [0, 64) of the S buffer: every thread has read its scores (A_LOADED, above)
-                if (sub) dq_half_finish<kF16>(sv, gv, c_edge, packed);
-                else dq_half_finish_scaled<kF16>(sv, gv, c_edge, mul, packed);
+                dq_half_finish<kF16>(sv, gv, c_edge, packed);
                 tmem_st16(lane_base + kColS + 128 * buf + 16 * kq, packed);
                 tmem_wait_st();
                 tc_fence_before();

@@ -346,8 +346,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
                 if (r == 0) SB_TRACE_EV(c, 1 + b, 4);
                 if (cw) {
-                    cw[carry_slot(wk.slot_base, wk.qt, 2 * kt + 1) * kTileQ] = Win;
-                    cw[carry_slot(wk.slot_base, wk.qt, 2 * kt) * kTileQ] = Win * f[8];
+                    // the carry at the right edge of every 32-key quarter of the tile
+                    const int64_t s0 = carry_slot32(wk.slot_base, wk.qt, 4 * kt) * kTileQ;
+                    cw[s0 + 3 * kTileQ] = Win;
+                    cw[s0 + 2 * kTileQ] = Win * f[12];
+                    cw[s0 + kTileQ] = Win * f[8];
+                    cw[s0] = Win * f[4];
                 }
                 fwd_finish<kF16>(u3, f + 12, Win, packed);
                 tmem_st16(s_base + kColPOff + 48, packed);

@@ -165,7 +165,7 @@ def workspace_bytes(batched, n_seqs, heads, tokens, max_seqlens, save_carries=Tr
     off = up(off + 16 * n_seqs)             # sequence table
     off = up(off + 8 * max_items)           # item table
     off = up(off + 4 * 2 * (n_max + 2))     # histogram scratch
-    carry = 4 * heads * slot_cap * tile
+    carry = 4 * heads * 2 * slot_cap * tile  # two 32-key carries per 64-key slot
     drem = 4 * heads * tokens * (n_seqs if batched else 1)  # drem + do . v per row (fused-remainder backward)
     return off + (carry if save_carries else 0), up(carry) + up(drem)
 

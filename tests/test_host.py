@@ -68,8 +68,8 @@ def test_workspace_sizes(lib):
     fb, bb = ctypes.c_size_t(), ctypes.c_size_t()
     p = params()
     assert lib.sbattn_workspace_bytes(ctypes.byref(p), ctypes.byref(fb), ctypes.byref(bb)) == 0
-    # items <= T/128 + S = 11, tiles per sequence <= 4: slots <= 11*5, 128 floats each, per head
-    carry = 4 * 11 * 5 * 128 * 4
+    # items <= T/128 + S = 11, tiles per sequence <= 4: 64-key slots <= 11*5, two 32-key carries of 128 floats each, per head
+    carry = 4 * 11 * 5 * 2 * 128 * 4
     rows = 4 * 1024 * 4  # one float per (head, token): drem + do . v of the fused-remainder backward
     assert bb.value == carry + rows and fb.value > carry
     p.save_carries = 0
