@@ -380,6 +380,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_wait_ld();
                 tc_fence_before();
                 mbar_arrive(&bars[A_LOADED]);  // dP is free; so are the S columns that dS will overwrite, once all have arrived
+                if (j + 1 < n) prefetch_l2(cw + slot + 4 * kTileQ);  // the next step's carry on its way into the L2
                 if (masked) dq_half_pass1<true>(sv, gv, scale, 32 * sub, lim, drem, W);
                 else dq_half_pass1<false>(sv, gv, scale, 32 * sub, lim, drem, W);
                 float cl = 0.f;  // prefix of g inside the quarter
@@ -441,12 +442,12 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 // ================================================================================================ dk/dv kernel
-// One block per SM (384 threads) keeps a 128-key tile stationary and walks the 128-row query tiles below it.  All four
-// contractions run with M = 128 and N = 128 (N = D for the last two), the widest shape that 512 columns of tensor
-// memory allow: S and dP [128 q x 128 keys], dv and dk [128 keys x D] (an MMA instruction costs the same ~65 cycles for N = 64
-// and N = 128, so narrow tiles waste half of the tensor pipe).  Tensor memory is full with these four, so S and dP cannot
-// be double-buffered; the step is pipelined another way:
-//   * a row thread copies its 64 scores and 64 dP values to registers as soon as they exist and releases S / dP at once,
+// One block per SM (608 threads, at most 104 registers each) keeps a 128-key tile stationary and walks the 128-row query
+// tiles below it.  All four contractions run with M = 128 and N = 128 (N = D for the last two), the widest shape that 512
+// columns of tensor memory allow: S and dP [128 q x 128 keys], dv and dk [128 keys x D] (an MMA instruction costs the same
+// ~65 cycles for N = 64 and N = 128, so narrow tiles waste half of the tensor pipe).  Tensor memory is full with these
+// four, so S and dP cannot be double-buffered; the step is pipelined another way:
+//   * a row thread copies its 32 scores and 32 dP values to registers as soon as they exist and releases S / dP at once,
 //     so the tensor cores compute S, dP of the next query tile while the threads work on this one;
 //   * the row threads form two halves by query row (rows 0-63 / 64-127).  dv += p^T do and dk += ds^T q reduce
 //     over query rows, so each half contributes its own four k-steps; the halves share ONE pair of p / ds buffers of
@@ -454,17 +455,17 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 //   * Q and dO are loaded twice from the L2: whole tiles one step early for S, dP (one slot each), and as 64-row halves
 //     just in time for dk, dv (one slot per half).  Holding a tile from its first use to its last would need three
 //     slots per operand, which shared memory does not have;
-//   * the steps of all items form one stream: S, dP of the first step of the next item are computed while the last step
-//     of this one is still being worked on, and dk, dv of a finished item are stored in the middle of the next item's
-//     first step.
-// Inside a half, warps of group 0 own the right 64 keys of the tile and warps of group 1 the left 64 keys (independent,
-// because carry_w / carry_c exist at every 64-key boundary).  Warp 8 loads K, V (once per item) and the early Q, dO
-// tiles, warp 10 the late halves, warp 11 fetches the per-row scalars of the next step (carry_w, carry_c, drem) into
-// shared memory, warp 9 issues every tcgen05.mma.
-constexpr int kKvThreads = 384;
+//   * across items the issuing warp orders the contractions as: last dV, dK of the item, then the wait for the next item's
+//     K, V and its first S, dP, which run while the row threads store dk, dv.
+// Sixteen row warps: a thread owns one query row and a quarter (32 keys) of the tile, warps 0-3 the rightmost quarter ...
+// warps 12-15 the leftmost; every quarter is entered independently with carry_w and carry_c of its right edge (both exist
+// at every 32-key boundary), which the thread loads itself at the top of the step: with four row warps per scheduler the
+// latency is covered.  Warp 16 loads K, V (once per item) and the early Q, dO tiles, warp 18 the late halves, warp 17
+// issues every tcgen05.mma.
+constexpr int kKvThreads = 608;
 constexpr int kKT = 128;  // keys per stationary tile
 enum KvBar { B_KV_FULL, B_KV_EMPTY, B_E_FULL, B_E_EMPTY, B_L_FULL0, B_L_FULL1, B_L_EMPTY0, B_L_EMPTY1, B_SDP_READY, B_LOADED,
-             B_PDS_READY0, B_PDS_READY1, B_PDS_FREE0, B_PDS_FREE1, B_SC_FULL, B_DKV_READY, B_DKV_FREE, B_WORK_FULL0,
+             B_PDS_READY0, B_PDS_READY1, B_PDS_FREE0, B_PDS_FREE1, B_DKV_READY, B_DKV_FREE, B_WORK_FULL0,
              B_WORK_FULL1, B_WORK_EMPTY0, B_WORK_EMPTY1, kNumKvBars };
 
 struct KvWork {
@@ -517,11 +518,12 @@ __device__ __forceinline__ void kv_chunk(const uint32_t (&s)[32], const uint32_t
     }
 }
 
-// dk or dv of a finished item out of tensor memory: a thread holds one key row, the head dim along the columns.
+// dk or dv of a finished item out of tensor memory: a thread holds one key row and D / 2 columns of the head dim, from
+// chunk0 * 32 on.
 // Not inlined: it runs once per item, and inside the step loop it would only dilute the instruction cache.
 // With the fused remainder dv also receives rem * do of its own row: the direct path of out = o + rem * v.
 template <int D, bool kF16, bool kFused>
-__device__ __noinline__ void kv_store_rows(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr) {
+__device__ __noinline__ void kv_store_rows(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr, int chunk0) {
     tc_fence_after();
     const MatView m = is_dv ? a.dv : a.dk;
     const float sc = is_dv ? 1.f : a.inv_temp;
@@ -536,7 +538,8 @@ __device__ __noinline__ void kv_store_rows(const KArgs& a, bool is_dv, const KvW
         mul = kF16 ? __half2float(*(const __half*)rp) : __bfloat162float(*(const __nv_bfloat16*)rp);
     }
 #pragma unroll
-    for (int cidx = 0; cidx < D / 32; ++cidx) {
+    for (int cc = 0; cc < D / 64; ++cc) {  // this thread's half of the head dim, 32 columns at a time
+        const int cidx = chunk0 + cc;
         uint32_t v[32];
         tmem_ld32(taddr + cidx * 32, v);
         tmem_wait_ld();
@@ -580,29 +583,25 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint32_t* tmem_slot = (uint32_t*)(bars + kNumKvBars);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     SchedRing<KvWork>* ring = (SchedRing<KvWork>*)(tmem_slot + 2);
-    float* sc_w = (float*)(tmem_slot + 20);  // [key half][128 rows]: carry_w of the step
-    float* sc_c = sc_w + 256;                // [key half][128 rows]: carry_c of the step
-    float* sc_d = sc_c + 256;                // [128 rows]: drem of the step
     static_assert(sizeof(SchedRing<KvWork>) <= 72, "ring does not fit its place");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < kNumKvBars; ++i) {
             uint32_t cnt = 1;
-            if (i == B_LOADED || i == B_DKV_FREE) cnt = 256;
-            if (i == B_PDS_READY0 || i == B_PDS_READY1) cnt = 128;
-            if (i == B_SC_FULL) cnt = 32;
-            if (i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) cnt = 259;  // MMA warp (one lane), two producers, 256 row threads
+            if (i == B_LOADED || i == B_DKV_FREE) cnt = 512;
+            if (i == B_PDS_READY0 || i == B_PDS_READY1) cnt = 256;
+            if (i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) cnt = 514;  // MMA warp (one lane), late producer, 512 row threads
             mbar_init(&bars[i], cnt);
         }
         *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
         fence_barrier_init();
     }
-    if (warp == 9) {
+    if (warp == 17) {
         tmem_alloc(tmem_slot, kCols);
         tmem_relinquish();
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == 16 && lane == 0) {
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
@@ -618,7 +617,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int n_work = *abort_flag ? 0 : n_items * a.heads;
     // G counts query-tile steps over all items of this block; a barrier that completes once per step is in phase G & 1.
 
-    if (warp == 8) {
+    if (warp == 16) {
         // ------------------------------------------------------------------ TMA: K, V per item; Q, dO tiles for S, dP
         if (lane == 0) {
             uint32_t G = 0, items = 0;
@@ -649,7 +648,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 18) {
         // ------------------------------------------------------------------ TMA: 64-row halves of Q, dO for dk, dv
         if (lane == 0) {
             uint32_t G = 0;
@@ -675,60 +674,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
             }
         }
-    } else if (warp == 11) {
-        // ------------------------------------------------------------------ per-row scalars of the next step
-        // plain loads by a warp that has nothing else to do: the row threads never wait for global memory
-        uint32_t G = 0;
-        bool ok = true;
-        SchedConsumer sched;
-        int w;
-        KvWork wk;
-        while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk, lane == 0, true)) >= 0) {
-            const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ;
-            const float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ;
-            for (int i = wk.kt; i < wk.n_qt; ++i, ++G) {
-                float vw[2][4], vc[2][4], vd[4];
-#pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    const int r = m * 32 + lane, qi = i * kBM + r;
-                    const bool row_ok = qi < wk.len;
-                    vd[m] = 0.f;
-                    if (kFused) {  // drem + do . v, left behind by the dq kernel
-                        if (row_ok) vd[m] = a.drem_eff[(int64_t)wk.h * a.drem_rows + (int64_t)wk.b * a.tokens + wk.start + qi];
-                    } else if (row_ok) {
-                        const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh +
-                                                            (int64_t)(wk.start + qi) * a.d_rem.st);
-                        vd[m] = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
-                    }
-#pragma unroll
-                    for (int hf = 0; hf < 2; ++hf) {
-                        const int kh = 2 * wk.kt + hf;
-                        vw[hf][m] = 0.f;
-                        vc[hf][m] = 0.f;
-                        if (row_ok && kh * kBK < wk.len) {  // the half may lie beyond the end of the sequence
-                            const int64_t slot = carry_slot(wk.slot_base, i, kh) * kTileQ + r;
-                            vw[hf][m] = cw[slot];
-                            vc[hf][m] = cc[slot];
-                        }
-                    }
-                }
-                // every row thread has read the scalars of the previous step once it has arrived at B_LOADED
-                if (G > 0) ok = mbar_wait(&bars[B_LOADED], (G - 1) & 1, abort_flag);
-                if (!ok) break;
-#pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    const int r = m * 32 + lane;
-                    sc_d[r] = vd[m];
-#pragma unroll
-                    for (int hf = 0; hf < 2; ++hf) {
-                        sc_w[hf * 128 + r] = vw[hf][m];
-                        sc_c[hf * 128 + r] = vc[hf][m];
-                    }
-                }
-                mbar_arrive(&bars[B_SC_FULL]);
-            }
-        }
-    } else if (warp == 9) {
+    } else if (warp == 17) {
         // ------------------------------------------------------------------ MMA issuer
         {
             const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
@@ -825,9 +771,9 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
     } else {
         // ------------------------------------------------------------------ row threads
-        const int grp = warp >> 2;
-        const int hf = grp ^ 1;          // 64-key half of the tile this thread owns
-        const int hh = (warp & 3) >> 1;  // half of the query rows this thread belongs to
+        const int kq = 3 - (warp >> 2);        // 32-key quarter of the tile this thread owns
+        const int hf = kq >> 1, sub = kq & 1;  // its 64-key half (a block of the p / ds buffers, the unit of masking)
+        const int hh = (warp & 3) >> 1;        // half of the query rows this thread belongs to
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const float scale = a.inv_temp * kLog2e;
@@ -836,15 +782,15 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         uint32_t G = 0, items = 0;
         bool ok = true;
         SB_TRACE_DECL(c);
-        // dk (group 0) / dv (group 1) are stored when the item's last contractions are complete; S, dP of the next item's
-        // first step are computed meanwhile
+        // dk (even quarters) / dv (odd quarters) are stored when the item's last contractions are complete, half of the
+        // head dim per thread; S, dP of the next item's first step are computed meanwhile
         auto store_dkdv = [&](const KvWork& e, uint32_t item) {
             ok = mbar_wait(&bars[B_DKV_READY], item & 1, abort_flag);
             if (!ok) return;
-            if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 6);
-            kv_store_rows<D, kF16, kFused>(a, grp == 1, e, r, lane_base + (grp == 0 ? kColDK : kColDV));
+            if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 6);
+            kv_store_rows<D, kF16, kFused>(a, sub == 1, e, r, lane_base + (sub == 0 ? kColDK : kColDV), hf * (D / 64));
             mbar_arrive(&bars[B_DKV_FREE]);
-            if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 7);
+            if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 7);
         };
         SchedConsumer sched;
         int w;
@@ -852,56 +798,69 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk)) >= 0) {
             const int n = wk.n_qt - wk.kt;
             const int kh = 2 * wk.kt + hf;
+            const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
+            const float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
+            const bool half_ok = kh * kBK < wk.len;  // the half may lie beyond the end of the sequence
             for (int j = 0; j < n; ++j) {
                 const int i = wk.kt + j;
                 const uint32_t g = G + j;
                 const int qi = i * kBM + r;
-                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 1);
-                ok = mbar_wait(&bars[B_SC_FULL], g & 1, abort_flag);
-                if (!ok) break;
-                float W = sc_w[hf * 128 + r];
-                float c = sc_c[hf * 128 + r];  // prefix of g through the right edge of this half; loses every g it passes
-                const float drem = sc_d[r];
+                const bool row_ok = qi < wk.len;
+                // the scalars of the step: carry_w and the prefix of g at the quarter's right edge, drem of the row
+                float W = 0.f, c = 0.f, drem = 0.f;
+                if (row_ok) {
+                    if (half_ok) {
+                        const int64_t slot = carry_slot32(wk.slot_base, i, 4 * wk.kt + kq) * kTileQ;
+                        W = __ldg(cw + slot);
+                        c = __ldg(cc + slot);  // loses every g it passes
+                    }
+                    if (kFused) {  // drem + do . v, left behind by the dq kernel
+                        drem = __ldg(a.drem_eff + (int64_t)wk.h * a.drem_rows + (int64_t)wk.b * a.tokens + wk.start + qi);
+                    } else {
+                        const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh +
+                                                            (int64_t)(wk.start + qi) * a.d_rem.st);
+                        drem = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
+                    }
+                }
+                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 1);
                 ok = mbar_wait(&bars[B_SDP_READY], g & 1, abort_flag);
                 if (!ok) break;
-                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 2);
+                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 2);
                 tc_fence_after();
                 const bool masked = i == wk.kt;
                 const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
-                uint32_t pp[32], ps[32];
+                uint32_t pp[16], ps[16];
                 {
-                    uint32_t s1[32], d1[32], s0[32], d0[32];
-                    tmem_ld32(lane_base + kColS + 64 * hf + 32, s1);
-                    tmem_ld32(lane_base + kColDP + 64 * hf + 32, d1);
-                    tmem_ld32(lane_base + kColS + 64 * hf, s0);
-                    tmem_ld32(lane_base + kColDP + 64 * hf, d0);
+                    uint32_t s1[32], d1[32];
+                    tmem_ld32(lane_base + kColS + 32 * kq, s1);
+                    tmem_ld32(lane_base + kColDP + 32 * kq, d1);
                     tmem_wait_ld();
                     tc_fence_before();
-                    mbar_arrive(&bars[B_LOADED]);  // S, dP and the scalars of this step are free
-                    if (masked) {
-                        kv_chunk<true, kF16>(s1, d1, scale, 32, lim, drem, c, W, pp + 16, ps + 16);
-                        kv_chunk<true, kF16>(s0, d0, scale, 0, lim, drem, c, W, pp, ps);
-                    } else {
-                        kv_chunk<false, kF16>(s1, d1, scale, 32, lim, drem, c, W, pp + 16, ps + 16);
-                        kv_chunk<false, kF16>(s0, d0, scale, 0, lim, drem, c, W, pp, ps);
+                    mbar_arrive(&bars[B_LOADED]);  // S and dP of this step are free
+                    if (j + 1 < n && half_ok) {  // the next step's carries on their way into the L2
+                        const int64_t nslot = carry_slot32(wk.slot_base, i + 1, 4 * wk.kt + kq) * kTileQ;
+                        prefetch_l2(cw + nslot);
+                        prefetch_l2(cc + nslot);
                     }
+                    if (masked) kv_chunk<true, kF16>(s1, d1, scale, 32 * sub, lim, drem, c, W, pp, ps);
+                    else kv_chunk<false, kF16>(s1, d1, scale, 32 * sub, lim, drem, c, W, pp, ps);
                 }
-                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 3);
+                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 3);
                 // the p / ds buffers are free once the contractions of their previous use are complete: the other half's,
                 // of the previous step for half 0 and of this step for half 1 (one barrier per half, so that a waiter
                 // is never two phases away from the phase it names)
                 ok = mbar_wait(&bars[B_PDS_FREE0 + (hh ^ 1)], (g & 1) ^ (hh ^ 1), abort_flag);
                 if (!ok) break;
-                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 4);
+                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 4);
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    const int off = (ch ^ (r & 7)) << 4;
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int off = ((4 * sub + ch) ^ (r & 7)) << 4;
                     *(uint4*)(prow + off) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
                     *(uint4*)(srow + off) = make_uint4(ps[4 * ch], ps[4 * ch + 1], ps[4 * ch + 2], ps[4 * ch + 3]);
                 }
                 fence_async_smem();
                 mbar_arrive(&bars[B_PDS_READY0 + hh]);
-                if ((r & 63) == 0 && grp == 0) SB_TRACE_EV(c, 1 + hh, 5);
+                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 5);
             }
             if (!ok) break;
             store_dkdv(wk, items);
@@ -909,7 +868,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             ++items;
         }
     }
-    tc_teardown(abort_flag, a.status, tmem, kCols, 9);
+    tc_teardown(abort_flag, a.status, tmem, kCols, 17);
     sched_finish(a.sched + 4);
 }
 
