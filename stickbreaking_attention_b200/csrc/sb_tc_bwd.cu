@@ -801,14 +801,13 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const float* cw = a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             const float* cc = a.carry_c + ((int64_t)wk.h * a.slot_cap) * kTileQ + r;
             const bool half_ok = kh * kBK < wk.len;  // the half may lie beyond the end of the sequence
-            for (int j = 0; j < n; ++j) {
-                const int i = wk.kt + j;
-                const uint32_t g = G + j;
+            // the scalars of a step: carry_w and the prefix of g at the quarter's right edge, drem of the row.  Those of the
+            // next step are loaded after this step's arithmetic, so that they are in flight across the waits in between
+            // and occupy no register during the arithmetic.
+            const auto load_scalars = [&](int i, float& W, float& c, float& drem) {
                 const int qi = i * kBM + r;
-                const bool row_ok = qi < wk.len;
-                // the scalars of the step: carry_w and the prefix of g at the quarter's right edge, drem of the row
-                float W = 0.f, c = 0.f, drem = 0.f;
-                if (row_ok) {
+                W = 0.f; c = 0.f; drem = 0.f;
+                if (qi < wk.len) {
                     if (half_ok) {
                         const int64_t slot = carry_slot32(wk.slot_base, i, 4 * wk.kt + kq) * kTileQ;
                         W = __ldg(cw + slot);
@@ -822,6 +821,13 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         drem = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
                     }
                 }
+            };
+            float W, c, drem;
+            load_scalars(wk.kt, W, c, drem);
+            for (int j = 0; j < n; ++j) {
+                const int i = wk.kt + j;
+                const uint32_t g = G + j;
+                const int qi = i * kBM + r;
                 if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 1);
                 ok = mbar_wait(&bars[B_SDP_READY], g & 1, abort_flag);
                 if (!ok) break;
@@ -837,15 +843,11 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tmem_wait_ld();
                     tc_fence_before();
                     mbar_arrive(&bars[B_LOADED]);  // S and dP of this step are free
-                    if (j + 1 < n && half_ok) {  // the next step's carries on their way into the L2
-                        const int64_t nslot = carry_slot32(wk.slot_base, i + 1, 4 * wk.kt + kq) * kTileQ;
-                        prefetch_l2(cw + nslot);
-                        prefetch_l2(cc + nslot);
-                    }
                     if (masked) kv_chunk<true, kF16>(s1, d1, scale, 32 * sub, lim, drem, c, W, pp, ps);
                     else kv_chunk<false, kF16>(s1, d1, scale, 32 * sub, lim, drem, c, W, pp, ps);
                 }
                 if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 3);
+                if (j + 1 < n) load_scalars(i + 1, W, c, drem);
                 // the p / ds buffers are free once the contractions of their previous use are complete: the other half's,
                 // of the previous step for half 0 and of this step for half 1 (one barrier per half, so that a waiter
                 // is never two phases away from the phase it names)
