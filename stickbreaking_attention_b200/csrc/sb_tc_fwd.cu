@@ -30,15 +30,15 @@ using namespace sm100;
 
 namespace {
 
-constexpr int kFwdThreads = 352;
+constexpr int kFwdThreads = 608;
 constexpr int kBM = 128, kBN = 128;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColO = 384, kColPOff = 64;  // S buffer i at 128*i (i = step mod 3), its P at +64
 constexpr int kKStages = 3, kVStages = 2;
 enum FwdBar { Q_FULL, Q_EMPTY, K_FULL0, K_FULL1, K_FULL2, K_EMPTY0, K_EMPTY1, K_EMPTY2, V_FULL0, V_FULL1, V_EMPTY0, V_EMPTY1, S_READY0, S_READY1,
               S_READY2, P_READY0, P_READY1, P_READY2, O_READY, O_FREE, WORK_FULL0, WORK_FULL1, WORK_EMPTY0, WORK_EMPTY1,
-              X_W0,  // 8 barriers: [group][warp of the group]
-              kNumBars = X_W0 + 8 };
+              X_W0,  // 32 barriers for the carry chain: [quarter][tile parity][warp & 3]
+              kNumBars = X_W0 + 32 };
 
 // With e = exp(s) and d = 1 + e:  beta = e / d,  1 - beta = 1 / d.  For key m of a group of 8 keys entered with the
 // carry W (product of 1 - beta over everything to its right)
@@ -103,27 +103,27 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     SchedRing<Work>* ring = (SchedRing<Work>*)(bars + kNumBars);
     uint32_t* tmem_slot = (uint32_t*)(ring + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* xw = (float*)(tmem_slot + 4);  // [group][128 rows]: carry leaving the tile the group has just swept
-    float* wfin = xw + 256;               // [item parity][128 rows]: remainder of the row, for the fused epilogue of both groups
+    float* xw = (float*)(tmem_slot + 4);  // [quarter][128 rows]: carry leaving the quarter its thread has just swept
+    float* wfin = xw + 512;               // [item parity][128 rows]: remainder of the row, for the fused epilogue of both groups
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i) {
             uint32_t cnt = 1;
-            if (i == P_READY0 || i == P_READY1 || i == P_READY2) cnt = 128;
-            if (i >= X_W0) cnt = 32;  // a warp waits for the warp that holds the same rows in the other group
-            if (i == O_FREE) cnt = 256;
-            if (i == WORK_EMPTY0 || i == WORK_EMPTY1) cnt = 258;  // MMA thread, V producer, 256 row threads
+            if (i == P_READY0 || i == P_READY1 || i == P_READY2) cnt = 512;
+            if (i >= X_W0) cnt = 32;  // a warp waits for the warp that holds the same rows in the quarter to its right
+            if (i == O_FREE) cnt = 512;
+            if (i == WORK_EMPTY0 || i == WORK_EMPTY1) cnt = 514;  // MMA thread, V producer, 512 row threads
             mbar_init(&bars[i], cnt);
         }
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 9) {
+    if (warp == 17) {
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == 16 && lane == 0) {
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
@@ -135,7 +135,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const int n_items = a.hdr->n_items;
     const int n_work = n_items * a.heads;
 
-    if (warp == 8) {
+    if (warp == 16) {
         // ------------------------------------------------------------------ TMA producer: Q and K
         if (lane == 0) {
             uint32_t ph_qe = 1, ph_ke = 7;  // "empty" barriers start released; bit i of ph_ke: K stage i
@@ -166,7 +166,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 18) {
         // ------------------------------------------------------------------ TMA producer: V
         if (lane == 0) {
             uint32_t ph_ve0 = 1, ph_ve1 = 1;
@@ -190,7 +190,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == 17) {
         // ------------------------------------------------------------------ MMA issuer
         {
             const bool leader = elect_one();  // the whole warp runs the loops; one lane issues
@@ -275,15 +275,13 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             }
         }
     } else {
-        // ------------------------------------------------------------------ row groups
-        const int b = warp >> 2;               // group
+        // ------------------------------------------------------------------ row threads: warps 0-3 rightmost quarter ... 12-15 leftmost
+        const int kq = 3 - (warp >> 2);        // 32-key quarter of every tile this thread owns
         const int r = (warp & 3) * 32 + lane;  // row of the tile == TMEM lane
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         uint32_t step = 0;   // key tiles of all items so far: tile number g uses S buffer g % 3 for the (g / 3)-th time
         const float scale = a.inv_temp * kLog2e;
-        float* x_mine = xw + b * 128;
-        const float* x_other = xw + (b ^ 1) * 128;
-        uint32_t ph_o = 0, ph_x = 0, items = 0;
+        uint32_t ph_o = 0, items = 0;
         bool ok = true;
         SB_TRACE_DECL(c);
         SchedConsumer sched;
@@ -295,107 +293,83 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             const bool row_ok = qi < wk.len;
             float* cw = a.carry_w ? a.carry_w + ((int64_t)wk.h * a.slot_cap) * kTileQ + r : nullptr;
             const int lim = a.attend_current ? r + 1 : r;  // diagonal tile: columns < lim are visible
-            float W = 1.f;  // carry leaving the last tile this thread swept
-            for (int j = b; j < n; j += 2) {
+            float W = 1.f;  // carry leaving the last quarter this thread swept
+            for (int j = 0; j < n; ++j) {
                 const int kt = wk.qt - j;
                 const uint32_t g = step + j, sb = g % 3;
                 const uint32_t s_base = lane_base + kColS0 + 128 * sb;
-                if (r == 0) SB_TRACE_EV(c, 1 + b, 1);
-                // both groups wait on the barriers of a buffer in turn: the parity follows from the use count
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 1);
                 ok = mbar_wait(&bars[S_READY0 + sb], (g / 3) & 1, abort_flag);
                 if (!ok) break;
-                if (r == 0) SB_TRACE_EV(c, 1 + b, 2);
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 2);
                 tc_fence_after();
-                // sweep the row right to left relative to an entering carry of 1
-                uint32_t u3[32], u2[32], u1[32], u0[32], packed[16];
-                float run[4], f[16];
+                // sweep the quarter right to left relative to an entering carry of 1
+                uint32_t u[32], packed[16];
+                float run[4], f[4];
                 float Wl = 1.f;
-                tmem_ld32(s_base + 96, u3);
-                tmem_ld32(s_base + 64, u2);
+                tmem_ld32(s_base + 32 * kq, u);
                 tmem_wait_ld();
-                tmem_ld32(s_base + 32, u1);
-                tmem_ld32(s_base + 0, u0);
-                if (j == 0) {
-                    fwd_sweep<true>(u3, scale, 96, lim, run); fwd_carries(run, Wl, f + 12);
-                    fwd_sweep<true>(u2, scale, 64, lim, run); fwd_carries(run, Wl, f + 8);
-                    tmem_wait_ld();
-                    fwd_sweep<true>(u1, scale, 32, lim, run); fwd_carries(run, Wl, f + 4);
-                    fwd_sweep<true>(u0, scale, 0, lim, run); fwd_carries(run, Wl, f + 0);
-                } else {
-                    fwd_sweep<false>(u3, scale, 96, lim, run); fwd_carries(run, Wl, f + 12);
-                    fwd_sweep<false>(u2, scale, 64, lim, run); fwd_carries(run, Wl, f + 8);
-                    tmem_wait_ld();
-                    fwd_sweep<false>(u1, scale, 32, lim, run); fwd_carries(run, Wl, f + 4);
-                    fwd_sweep<false>(u0, scale, 0, lim, run); fwd_carries(run, Wl, f + 0);
-                }
-                if (r == 0) SB_TRACE_EV(c, 1 + b, 3);
-                // the true entering carry comes from the partner thread, which swept the tile to the right
+                if (j == 0) fwd_sweep<true>(u, scale, 32 * kq, lim, run);
+                else fwd_sweep<false>(u, scale, 32 * kq, lim, run);
+                fwd_carries(run, Wl, f);
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 3);
+                // The true entering carry travels along the row as a chain through shared memory: a thread takes it from
+                // the quarter to its right (the rightmost quarter from the leftmost one of the previous tile), multiplies
+                // by its own product and passes it on.  Nobody waits for a quarter to its left, so the quarters settle into
+                // a stagger.  The chain also orders the accesses to the S buffer: P of a quarter overwrites scores of
+                // quarters to its right only (kColPOff = 64), whose threads have loaded them before they passed the carry.
                 float Win = 1.f;
-                if (j > 0) {
-                    ok = mbar_wait(&bars[X_W0 + 4 * (b ^ 1) + (warp & 3)], ph_x, abort_flag);
-                    ph_x ^= 1;
+                if (kq < 3) {
+                    ok = mbar_wait(&bars[X_W0 + 8 * (kq + 1) + 4 * (g & 1) + (warp & 3)], (g >> 1) & 1, abort_flag);
                     if (!ok) break;
-                    Win = x_other[r];
+                    Win = xw[(kq + 1) * 128 + r];
+                } else if (j > 0) {
+                    ok = mbar_wait(&bars[X_W0 + 4 * ((g - 1) & 1) + (warp & 3)], ((g - 1) >> 1) & 1, abort_flag);
+                    if (!ok) break;
+                    Win = xw[r];
                 }
                 W = Win * Wl;
-                if (j + 1 < n) {
-                    x_mine[r] = W;
-                    mbar_arrive(&bars[X_W0 + 4 * b + (warp & 3)]);
-                } else if (kFused) {
-                    wfin[(items & 1) * 128 + r] = W;  // visible to both groups once O_READY has completed
-                }
-                if (r == 0) SB_TRACE_EV(c, 1 + b, 4);
-                if (cw) {
-                    // the carry at the right edge of every 32-key quarter of the tile
-                    const int64_t s0 = carry_slot32(wk.slot_base, wk.qt, 4 * kt) * kTileQ;
-                    cw[s0 + 3 * kTileQ] = Win;
-                    cw[s0 + 2 * kTileQ] = Win * f[12];
-                    cw[s0 + kTileQ] = Win * f[8];
-                    cw[s0] = Win * f[4];
-                }
-                fwd_finish<kF16>(u3, f + 12, Win, packed);
-                tmem_st16(s_base + kColPOff + 48, packed);
-                fwd_finish<kF16>(u2, f + 8, Win, packed);
-                tmem_st16(s_base + kColPOff + 32, packed);
-                fwd_finish<kF16>(u1, f + 4, Win, packed);
-                tmem_st16(s_base + kColPOff + 16, packed);
-                fwd_finish<kF16>(u0, f + 0, Win, packed);
-                tmem_st16(s_base + kColPOff + 0, packed);
+                xw[kq * 128 + r] = W;
+                mbar_arrive(&bars[X_W0 + 8 * kq + 4 * (g & 1) + (warp & 3)]);
+                if (kFused && kq == 0 && j + 1 == n) wfin[(items & 1) * 128 + r] = W;  // visible to all once O_READY has completed
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 4);
+                if (cw) cw[carry_slot32(wk.slot_base, wk.qt, 4 * kt + kq) * kTileQ] = Win;  // the carry at the quarter's right edge
+                fwd_finish<kF16>(u, f, Win, packed);
+                tmem_st16(s_base + kColPOff + 16 * kq, packed);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars[P_READY0 + sb]);
-                if (r == 0) SB_TRACE_EV(c, 1 + b, 5);
+                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 5);
             }
             if (!ok) break;
             step += n;
-            // epilogue: each group stores half of the head dim of every row
+            // epilogue: each quarter stores 32 columns of the head dim of every row
             ok = mbar_wait(&bars[O_READY], ph_o, abort_flag);
             ph_o ^= 1;
             if (!ok) break;
             tc_fence_after();
-            const int d0 = b * (D / 2);
-            char* orow = a.o.ptr + 2 * ((int64_t)wk.b * a.o.sb + (int64_t)wk.h * a.o.sh + (int64_t)(wk.start + qi) * a.o.st + d0);
-#pragma unroll
-            for (int c = 0; c < D / 64; ++c) {
+            if (kq < D / 32) {
+                const int d0 = kq * 32;
+                char* orow = a.o.ptr + 2 * ((int64_t)wk.b * a.o.sb + (int64_t)wk.h * a.o.sh + (int64_t)(wk.start + qi) * a.o.st + d0);
                 uint32_t v[32];
-                tmem_ld32(lane_base + kColO + d0 + c * 32, v);
+                tmem_ld32(lane_base + kColO + d0, v);
                 tmem_wait_ld();
                 if (row_ok) {
                     if (kFused) {  // out = o + rem * v, rem rounded to the output type first
                         const float remf = round16<kF16>(wfin[(items & 1) * 128 + r]);
                         float x[32];
                         load_row32<kF16>(a.v.ptr + 2 * ((int64_t)wk.b * a.v.sb + (int64_t)wk.h * a.v.sh +
-                                                         (int64_t)(wk.start + qi) * a.v.st + d0) + c * 64, x);
+                                                         (int64_t)(wk.start + qi) * a.v.st + d0), x);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(fmaf(remf, x[i], __uint_as_float(v[i])));
                     }
-                    store_row32<kF16>(orow + c * 64, v, 1.f);
+                    store_row32<kF16>(orow, v, 1.f);
                 }
             }
             tc_fence_before();
             mbar_arrive(&bars[O_FREE]);
             ++items;
-            if (row_ok && ((n - 1) & 1) == b) {  // this group swept the leftmost tile: W is the remainder of the row
+            if (row_ok && kq == 0) {  // this thread swept the leftmost quarter: W is the remainder of the row
                 const int64_t t = wk.start + qi;
                 char* rp = a.rem.ptr + 2 * ((int64_t)wk.b * a.rem.sb + (int64_t)wk.h * a.rem.sh + t * a.rem.st);
                 if (kF16) *(__half*)rp = __float2half_rn(W);
@@ -404,7 +378,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             }
         }
     }
-    tc_teardown(abort_flag, a.status, tmem, kTmemCols, 9);
+    tc_teardown(abort_flag, a.status, tmem, kTmemCols, 17);
     sched_finish(a.sched + 0);
 }
 
@@ -418,7 +392,7 @@ int launch_fwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         encode_tile_map(&mv, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBN))
         return 1;
     // Q + three K stages + two V stages; at least 120 KB so that one block owns the SM and its tensor memory
-    constexpr int need = (1 + kKStages + kVStages) * kBM * D * 2 + 1024 + 3072;
+    constexpr int need = (1 + kKStages + kVStages) * kBM * D * 2 + 1024 + 5120;  // tiles, alignment, barriers and exchange slots
     constexpr int smem = need > 120 * 1024 ? need : 120 * 1024;
     if (a.fused) {
         cudaError_t ef = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
