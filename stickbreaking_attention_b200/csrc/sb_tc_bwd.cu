@@ -804,26 +804,33 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // the scalars of a step: carry_w and the prefix of g at the quarter's right edge, drem of the row.  Those of the
             // next step are loaded after this step's arithmetic, so that they are in flight across the waits in between
             // and occupy no register during the arithmetic.
-            const auto load_scalars = [&](int i, float& W, float& c, float& drem) {
+            // (drem stays in its 16-bit form until it is used: a conversion right behind the load would stall the warp
+            // until the value has arrived)
+            const auto load_scalars = [&](int i, float& W, float& c, uint32_t& drem) {
                 const int qi = i * kBM + r;
-                W = 0.f; c = 0.f; drem = 0.f;
+                W = 0.f; c = 0.f; drem = 0u;
                 if (qi < wk.len) {
                     if (half_ok) {
                         const int64_t slot = carry_slot32(wk.slot_base, i, 4 * wk.kt + kq) * kTileQ;
                         W = __ldg(cw + slot);
                         c = __ldg(cc + slot);  // loses every g it passes
                     }
-                    if (kFused) {  // drem + do . v, left behind by the dq kernel
-                        drem = __ldg(a.drem_eff + (int64_t)wk.h * a.drem_rows + (int64_t)wk.b * a.tokens + wk.start + qi);
+                    if (kFused) {  // drem + do . v (float32), left behind by the dq kernel
+                        drem = __ldg((const uint32_t*)a.drem_eff + (int64_t)wk.h * a.drem_rows + (int64_t)wk.b * a.tokens + wk.start + qi);
                     } else {
                         const char* dp = a.d_rem.ptr + 2 * ((int64_t)wk.b * a.d_rem.sb + (int64_t)wk.h * a.d_rem.sh +
                                                             (int64_t)(wk.start + qi) * a.d_rem.st);
-                        drem = kF16 ? __half2float(*(const __half*)dp) : __bfloat162float(*(const __nv_bfloat16*)dp);
+                        drem = __ldg((const unsigned short*)dp);
                     }
                 }
             };
-            float W, c, drem;
-            load_scalars(wk.kt, W, c, drem);
+            const auto drem_value = [](uint32_t raw) {
+                if (kFused) return __uint_as_float(raw);
+                return kF16 ? __half2float(__ushort_as_half((unsigned short)raw)) : __uint_as_float(raw << 16);
+            };
+            float W, c;
+            uint32_t drem_raw;
+            load_scalars(wk.kt, W, c, drem_raw);
             for (int j = 0; j < n; ++j) {
                 const int i = wk.kt + j;
                 const uint32_t g = G + j;
@@ -843,11 +850,12 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tmem_wait_ld();
                     tc_fence_before();
                     mbar_arrive(&bars[B_LOADED]);  // S and dP of this step are free
+                    const float drem = drem_value(drem_raw);
                     if (masked) kv_chunk<true, kF16>(s1, d1, scale, 32 * sub, lim, drem, c, W, pp, ps);
                     else kv_chunk<false, kF16>(s1, d1, scale, 32 * sub, lim, drem, c, W, pp, ps);
                 }
                 if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 3);
-                if (j + 1 < n) load_scalars(i + 1, W, c, drem);
+                if (j + 1 < n) load_scalars(i + 1, W, c, drem_raw);
                 // the p / ds buffers are free once the contractions of their previous use are complete: the other half's,
                 // of the previous step for half 0 and of this step for half 1 (one barrier per half, so that a waiter
                 // is never two phases away from the phase it names)
