@@ -451,7 +451,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 //     so the tensor cores compute S, dP of the next query tile while the threads work on this one;
 //   * the row threads form two halves by query row (rows 0-63 / 64-127).  dv += p^T do and dk += ds^T q reduce
 //     over query rows, so each half contributes its own four k-steps; the halves share ONE pair of p / ds buffers of
-//     64 rows and take turns, which settles into a stagger of about a third of a step;
+//     64 rows and take turns.  The buffers are two regions of 32 rows that are written and consumed alternately, four
+//     contraction batches per step;
 //   * Q and dO are loaded twice from the L2: whole tiles one step early for S, dP (one slot each), and as 64-row halves
 //     just in time for dk, dv (one slot per half).  Holding a tile from its first use to its last would need three
 //     slots per operand, which shared memory does not have;
@@ -465,7 +466,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 constexpr int kKvThreads = 608;
 constexpr int kKT = 128;  // keys per stationary tile
 enum KvBar { B_KV_FULL, B_KV_EMPTY, B_E_FULL, B_E_EMPTY, B_L_FULL0, B_L_FULL1, B_L_EMPTY0, B_L_EMPTY1, B_SDP_READY, B_LOADED,
-             B_PDS_READY0, B_PDS_READY1, B_PDS_FREE0, B_PDS_FREE1, B_DKV_READY, B_DKV_FREE, B_WORK_FULL0,
+             B_PDS_READY0, B_PDS_READY1, B_PDS_FREE0, B_PDS_FREE1, B_PDS_FREE2, B_PDS_FREE3, B_DKV_READY, B_DKV_FREE, B_WORK_FULL0,
              B_WORK_FULL1, B_WORK_EMPTY0, B_WORK_EMPTY1, kNumKvBars };
 
 struct KvWork {
@@ -590,7 +591,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int i = 0; i < kNumKvBars; ++i) {
             uint32_t cnt = 1;
             if (i == B_LOADED || i == B_DKV_FREE) cnt = 512;
-            if (i == B_PDS_READY0 || i == B_PDS_READY1) cnt = 256;
+            if (i == B_PDS_READY0 || i == B_PDS_READY1) cnt = 128;  // the four warps of 32 query rows
             if (i == B_WORK_EMPTY0 || i == B_WORK_EMPTY1) cnt = 514;  // MMA warp (one lane), late producer, 512 row threads
             mbar_init(&bars[i], cnt);
         }
@@ -732,29 +733,24 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         have = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, nx, leader, true) >= 0;
                     }
 #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
+                    for (int i = 0; i < 4; ++i) {  // 32 query rows at a time: region i & 1 of the p / ds buffers
+                        const int hh = i >> 1, b = i & 1;
                         SB_TRACE_EV(m, 0, 3 + 2 * hh);
-                        ok = mbar_wait(&bars[B_PDS_READY0 + hh], g & 1, abort_flag) &&
-                             mbar_wait(&bars[B_L_FULL0 + hh], g & 1, abort_flag);
-                        if (ok && j == 0 && hh == 0)  // the previous item's accumulators must have been read out
+                        ok = mbar_wait(&bars[B_PDS_READY0 + b], hh, abort_flag);  // a region is used twice per step
+                        if (ok && b == 0) ok = mbar_wait(&bars[B_L_FULL0 + hh], g & 1, abort_flag);
+                        if (ok && j == 0 && i == 0)  // the previous item's accumulators must have been read out
                             ok = mbar_wait(&bars[B_DKV_FREE], (items & 1) ^ 1, abort_flag);
                         if (!ok) break;
                         SB_TRACE_EV(m, 0, 4 + 2 * hh);
                         tc_fence_after();
                         const SmemDesc ddo = {desc_domn.lo + hh * (kHalfBytes >> 4), desc_domn.hi};
                         const SmemDesc dq = {desc_qmn.lo + hh * (kHalfBytes >> 4), desc_qmn.hi};
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            if (kk == 0) mma_ss_dyn(leader, tmem + kColDV, desc_p, 0, ddo, 0, idesc_t, j > 0 || hh > 0);
-                            else mma_ss<true>(leader, tmem + kColDV, desc_p, kk * 2048, ddo, kk * 2048, idesc_t);
-                        }
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            if (kk == 0) mma_ss_dyn(leader, tmem + kColDK, desc_ds, 0, dq, 0, idesc_t, j > 0 || hh > 0);
-                            else mma_ss<true>(leader, tmem + kColDK, desc_ds, kk * 2048, dq, kk * 2048, idesc_t);
-                        }
-                        mma_commit(leader, &bars[B_PDS_FREE0 + hh]);
-                        mma_commit(leader, &bars[B_L_EMPTY0 + hh]);
+                        mma_ss_dyn(leader, tmem + kColDV, desc_p, b * 4096, ddo, b * 4096, idesc_t, j > 0 || i > 0);
+                        mma_ss<true>(leader, tmem + kColDV, desc_p, b * 4096 + 2048, ddo, b * 4096 + 2048, idesc_t);
+                        mma_ss_dyn(leader, tmem + kColDK, desc_ds, b * 4096, dq, b * 4096, idesc_t, j > 0 || i > 0);
+                        mma_ss<true>(leader, tmem + kColDK, desc_ds, b * 4096 + 2048, dq, b * 4096 + 2048, idesc_t);
+                        mma_commit(leader, &bars[B_PDS_FREE0 + 2 * b + hh]);
+                        if (b == 1) mma_commit(leader, &bars[B_L_EMPTY0 + hh]);
                     }
                 }
                 if (!ok) break;
@@ -856,10 +852,15 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 3);
                 if (j + 1 < n) load_scalars(i + 1, W, c, drem_raw);
-                // the p / ds buffers are free once the contractions of their previous use are complete: the other half's,
-                // of the previous step for half 0 and of this step for half 1 (one barrier per half, so that a waiter
-                // is never two phases away from the phase it names)
-                ok = mbar_wait(&bars[B_PDS_FREE0 + (hh ^ 1)], (g & 1) ^ (hh ^ 1), abort_flag);
+                // The 64-row p / ds buffers are two regions of 32 rows, each used by one warp quartet of either row half
+                // in turn (rows 0-31 and 64-95 the first region, 32-63 and 96-127 the second).  A region is free once the
+                // contractions of its previous use are complete: the other half's, of the previous step for half 0 and of
+                // this step for half 1.  While one region is consumed the other is written, so the contractions of a step
+                // follow each other without waiting for the row threads.  One "free" barrier per region and half, completing
+                // once per step, and a thread waits for the other half's: a waiter is never two phases away from the phase
+                // it names (with one barrier per region, completing twice per step, a thread of half 0 could arrive while
+                // its own previous use was still pending and mistake the completion before that for the one it wants).
+                ok = mbar_wait(&bars[B_PDS_FREE0 + 2 * (warp & 1) + (hh ^ 1)], (g & 1) ^ (hh ^ 1), abort_flag);
                 if (!ok) break;
                 if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 4);
 #pragma unroll
@@ -869,7 +870,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     *(uint4*)(srow + off) = make_uint4(ps[4 * ch], ps[4 * ch + 1], ps[4 * ch + 2], ps[4 * ch + 3]);
                 }
                 fence_async_smem();
-                mbar_arrive(&bars[B_PDS_READY0 + hh]);
+                mbar_arrive(&bars[B_PDS_READY0 + (warp & 1)]);
                 if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 5);
             }
             if (!ok) break;
