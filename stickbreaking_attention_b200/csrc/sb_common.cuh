@@ -12,7 +12,7 @@
 namespace sb {
 
 constexpr int kTileQ = 128;    // query rows per work item
-constexpr int kTileKV = 64;    // keys per carry slot: carries are kept at every 64-key boundary
+constexpr int kTileKV = 64;    // keys per slot of the slot count (each slot holds two 32-key carries)
 constexpr int kMaxHeadDim = 128;
 
 // One sequence of the pack (or one batch entry of the batched layout).

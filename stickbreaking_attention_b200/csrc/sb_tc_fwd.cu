@@ -1,5 +1,5 @@
-// Tensor-core forward (sm_100a): o, rem, neg_log_acc and the per-64-key carries of W for bf16 / f16 inputs with
-// head_dim 64 or 128.
+// Tensor-core forward (sm_100a): o, rem, neg_log_acc and the carries of W at every 32-key boundary for bf16 / f16 inputs
+// with head_dim 64 or 128.
 //
 // One work item = (head, sequence, 128-row query tile); one persistent thread block per SM draws items from a global
 // counter (heaviest first, interleaved over small groups of heads so that their K and V stay in L2).  Per item the key
@@ -7,21 +7,22 @@
 // (stickbreaking_attention/sb_varlen/sb_varlen_fwd.py:155-193) -- because the weight of key j needs the product of
 // (1 - beta) over the keys to its right.
 //
-// Warps of a block (352 threads):
-//   0-3 / 4-7  row group 0 / 1, one thread per query row in each.  The groups take the key tiles of an item in turn
-//              (group 0 the 1st, 3rd, ... tile from the diagonal, group 1 the others).  S lives in three rotating
-//              buffers in tensor memory, so the tensor cores are always two tiles ahead: while the groups turn
-//              scores into weights on the CUDA cores, S of later tiles and O += P V of earlier ones are in flight.
-//              A thread reads the 128 scores of its row, computes the weights RELATIVE to a carry of 1, receives the
-//              true carry W (product of 1 - beta over everything to the right of the tile) from its partner thread
-//              in the other group through shared memory, passes its own on, rescales, and writes the weights back to
-//              tensor memory as 16-bit operands.
-//   8 / 10     TMA producers: warp 8 loads Q once per item and the K tiles (three-stage ring, S runs ahead), warp 10
+// Warps of a block (608 threads, at most 104 registers each):
+//   0-15       row warps: a thread owns one query row and a quarter (32 keys) of every tile, warps 0-3 the rightmost
+//              quarter ... warps 12-15 the leftmost, so that every scheduler has four row warps to choose from.
+//              S lives in three rotating buffers in tensor memory, so the tensor cores are always two tiles ahead:
+//              while the threads turn scores into weights on the CUDA cores, S of later tiles and O += P V of earlier
+//              ones are in flight.  A thread reads its 32 scores, computes the weights RELATIVE to a carry of 1, receives
+//              the true carry W (product of 1 - beta over everything to the right of its quarter) from the thread of the
+//              quarter to its right through shared memory (the rightmost quarter from the leftmost one of the previous
+//              tile), passes its own on, rescales, and writes the weights back to tensor memory as 16-bit operands.
+//   16 / 18    TMA producers: warp 16 loads Q once per item and the K tiles (three-stage ring, S runs ahead), warp 18
 //              the V tiles (two-stage ring).
-//   9          issues tcgen05.mma: S = Q K^T (both operands in shared memory) into the next S buffer of the rotation,
+//   17         issues tcgen05.mma: S = Q K^T (both operands in shared memory) into the next S buffer of the rotation,
 //              O += P V (P from tensor memory, V from shared memory).
 // Tensor memory (512 columns): S buffers at columns 0, 128, 256; O [384,384+D).  P overwrites the right half of its S
-// buffer after the whole row has been read.
+// buffer: the weights of a quarter land on scores of quarters to its right, whose threads have read them before they
+// passed the carry on.
 #include "sb_tc_common.cuh"
 
 namespace sb {
