@@ -164,6 +164,11 @@ int sbattn_version(void);
  * No counterpart in the reference. */
 size_t sbattn_params_size(void);
 
+/* Number of GPU kernels this library has launched in the calling process so far (all entry points, all devices).
+ * A benchmark reads it before and after a step to report how many kernels of the library the step ran.
+ * No counterpart in the reference. */
+unsigned long long sbattn_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif

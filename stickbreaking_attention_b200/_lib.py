@@ -39,7 +39,8 @@ class SbParams(ctypes.Structure):
 FLAG_FUSED_REMAINDER = 1
 
 EXPORTS = ("sbattn_workspace_bytes", "sbattn_fwd", "sbattn_bwd", "sbattn_strerror", "sbattn_version",
-           "sbattn_params_size", "sbattn_fwd_static", "sbattn_static_scratch_bytes", "sbattn_attention_weights")
+           "sbattn_params_size", "sbattn_fwd_static", "sbattn_static_scratch_bytes", "sbattn_attention_weights",
+           "sbattn_launch_count")
 
 _lib = None
 
@@ -71,6 +72,7 @@ def lib():
         L.sbattn_strerror.restype = ctypes.c_char_p
         L.sbattn_version.restype = ctypes.c_int
         L.sbattn_params_size.restype = ctypes.c_size_t
+        L.sbattn_launch_count.restype = ctypes.c_ulonglong
         L.sbattn_fwd_static.argtypes = [ctypes.POINTER(SbParams)]
         L.sbattn_fwd_static.restype = ctypes.c_int
         L.sbattn_static_scratch_bytes.restype = ctypes.c_size_t

@@ -3,6 +3,8 @@
 
 namespace sb {
 
+unsigned long long g_launch_count = 0;
+
 namespace {
 
 int check_mat(const SbMat& m, bool required) {
@@ -86,6 +88,8 @@ using namespace sb;
 extern "C" int sbattn_version(void) { return SBATTN_VERSION; }
 
 extern "C" size_t sbattn_params_size(void) { return sizeof(SbParams); }
+
+extern "C" unsigned long long sbattn_launch_count(void) { return __atomic_load_n(&g_launch_count, __ATOMIC_RELAXED); }
 
 extern "C" const char* sbattn_strerror(int code) {
     switch (code) {

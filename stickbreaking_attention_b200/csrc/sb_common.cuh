@@ -137,6 +137,10 @@ template <> __device__ inline float from_f32<float>(float x) { return x; }
 template <> __device__ inline __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <> __device__ inline __half from_f32<__half>(float x) { return __float2half_rn(x); }
 
+// Kernel launches made by the library in this process (sbattn_launch_count); every launch site calls count_launch().
+extern unsigned long long g_launch_count;
+inline void count_launch() { __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED); }
+
 // launchers implemented in the .cu files (each returns a cudaError_t as int)
 int launch_prep(const SbParams& p, const WsLayout& L, cudaStream_t st);
 int launch_zero_tail(const SbParams& p, const KArgs& a, cudaStream_t st);

@@ -137,6 +137,7 @@ int launch_zero_tail(const SbParams& p, const KArgs& a, cudaStream_t st) {
         zero_tail_kernel<__half><<<64, 256, 0, st>>>(a.hdr, a.dq, a.dk, a.dv, p.heads, p.tokens, p.head_dim);
     else
         zero_tail_kernel<__nv_bfloat16><<<64, 256, 0, st>>>(a.hdr, a.dq, a.dk, a.dv, p.heads, p.tokens, p.head_dim);
+    count_launch();
     return (int)cudaGetLastError();
 }
 
@@ -146,6 +147,7 @@ int launch_prep(const SbParams& p, const WsLayout& L, cudaStream_t st) {
     prep_kernel<<<1, kPrepThreads, 0, st>>>((WsHeader*)ws, (SeqInfo*)(ws + L.off_seqs), (int2*)(ws + L.off_items),
                                             (int32_t*)(ws + L.off_bins), p.cu_seqlens, p.cu_width, L.n_seqs, p.batch,
                                             p.tokens, max_len, L.n_max, L.max_items, L.slot_cap, p.status);
+    count_launch();
     return (int)cudaGetLastError();
 }
 

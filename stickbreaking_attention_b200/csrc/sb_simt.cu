@@ -436,6 +436,7 @@ int launch_fwd_t(const WsLayout& L, const KArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     dim3 grid(L.max_items, a.heads, 2);
     simt_fwd_kernel<T><<<grid, kThreads, smem, st>>>(a);
+    count_launch();
     return (int)cudaGetLastError();
 }
 
@@ -447,10 +448,16 @@ int launch_bwd_t(const WsLayout& L, const KArgs& a, int phases, cudaStream_t st)
     e = cudaFuncSetAttribute(simt_bwd_dkdv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(L.max_items, a.heads, 2);
-    if (phases != SBATTN_BWD_DKDV) simt_bwd_dq_kernel<T><<<grid, kThreads, smem, st>>>(a);
+    if (phases != SBATTN_BWD_DKDV) {
+        simt_bwd_dq_kernel<T><<<grid, kThreads, smem, st>>>(a);
+        count_launch();
+    }
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (phases != SBATTN_BWD_DQ) simt_bwd_dkdv_kernel<T><<<grid, kThreads, smem, st>>>(a);
+    if (phases != SBATTN_BWD_DQ) {
+        simt_bwd_dkdv_kernel<T><<<grid, kThreads, smem, st>>>(a);
+        count_launch();
+    }
     return (int)cudaGetLastError();
 }
 

@@ -5,16 +5,17 @@
 //   dq kernel     one work item = (head, sequence, 128-row query tile).  Walks the keys LEFT TO RIGHT in steps of 128,
 //                 the direction of the reference's _backward_one_row (sb_varlen_bwd.py:401-473), because
 //                 ds_ik = g_ik - beta_ik * (sum of g over keys <= k) needs a prefix over the keys.  The weights of a
-//                 64-key half need the product W of (1 - beta) over everything to its right: the forward saved that
-//                 value for every 64-key boundary (carry_w).  The kernel leaves the prefix of g through the right
-//                 edge of every 64-key half in carry_c for the second kernel.
+//                 32-key quarter need the product W of (1 - beta) over everything to its right: the forward saved that
+//                 value for every 32-key boundary (carry_w).  The kernel leaves the prefix of g through the right
+//                 edge of every 32-key quarter in carry_c for the second kernel.
 //   dk/dv kernel  one work item = (head, sequence, 128-key tile), kept stationary; walks the 128-row query tiles
-//                 below it.  Every (query tile, 64-key half) pair is entered directly with carry_w and carry_c, the
+//                 below it.  Every (query tile, 32-key quarter) pair is entered directly with carry_w and carry_c, the
 //                 weights and ds are recomputed, written to shared memory as 16-bit operands, and
 //                 dv += p^T do, dk += ds^T q accumulate in tensor memory for the whole walk; stored once.
 //
-// Both kernels: one persistent block per SM (warps 0-7: two groups of one thread per query row, then TMA producers and
-// one warp that issues tcgen05.mma), all 512 tensor-memory columns, work drawn from a global counter.
+// Both kernels: one persistent block of 608 threads per SM (warps 0-15: one thread per query row and 32-key quarter of
+// a step; warps 16 and 18: TMA producers; warp 17 issues tcgen05.mma), all 512 tensor-memory columns, work drawn from a
+// global counter.
 #include "sb_tc_common.cuh"
 
 namespace sb {
@@ -24,7 +25,7 @@ using namespace sm100;
 namespace {
 
 constexpr int kBM = 128;  // query rows per tile
-constexpr int kBK = 64;   // keys per carry slot: carry_w / carry_c exist at every 64-key boundary
+constexpr int kBK = 64;   // keys per half of a step: the unit of masking and a 128-byte row of the p / ds buffers
 constexpr int kQBox = 128 * 128;  // bytes of one TMA box of a 128-row tile (64 elements wide)
 constexpr int kKBox = 64 * 128;   // bytes of one TMA box of a 64-row tile
 
@@ -245,7 +246,6 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const SmemDesc desc_kmn = make_desc(smem_u32(sK), kQBox, 1024);  // K tile as MN-major operand of dQ
             uint32_t G = 0, items = 0;
             bool ok = true;
-            SB_TRACE_DECL(m);
             auto issue_s = [&](uint32_t g) {
                 const uint32_t kst = g % kDqKStages;
                 const SmemDesc dk = {desc_k.lo + kst * (kQBytes >> 4), desc_k.hi};
@@ -289,18 +289,15 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int j = 0; ok && j < n; ++j) {
                     const uint32_t g = G + j, kst = g % kDqKStages;
                     if (j + 1 < n) {  // dP of the next step as soon as this step's is in registers
-                        SB_TRACE_EV(m, 0, 1);
                         ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
                         issue_dp(g + 1, j + 2 == n);
                         if (!ok) break;
                     }
-                    SB_TRACE_EV(m, 0, 2);
                     ok = mbar_wait(&bars[A_DS_READY], g & 1, abort_flag);
                     if (ok && j == 0) ok = mbar_wait(&bars[A_DQ_FREE], (items & 1) ^ 1, abort_flag);  // previous dQ read out
                     if (!ok) break;
-                    SB_TRACE_EV(m, 0, 3);
                     tc_fence_after();
                     const SmemDesc dkmn = {desc_kmn.lo + kst * (kQBytes >> 4), desc_kmn.hi};
                     const uint32_t a_ds = tmem + kColS + 128 * (g & 1);
@@ -311,7 +308,6 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     }
                     mma_commit(leader, &bars[A_K_EMPTY0 + kst]);
                     if (j + 2 < n) issue_s(g + 2);  // into the buffer whose dS the contraction above reads: in order
-                    SB_TRACE_EV(m, 0, 4);
                 }
                 if (!ok) break;
                 mma_commit(leader, &bars[A_DQ_READY]);
@@ -328,7 +324,6 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const float scale = a.inv_temp * kLog2e;
         uint32_t G = 0, items = 0;
         bool ok = true;
-        SB_TRACE_DECL(c);
         SchedConsumer sched;
         int w;
         Work wk;
@@ -367,10 +362,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const int kh = 2 * j + hf;
                 const int64_t slot = carry_slot32(wk.slot_base, wk.qt, 4 * j + kq) * kTileQ;
                 float W = half_ok(j) ? __ldg(cw + slot) : 0.f;
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 1);
                 ok = mbar_wait(&bars[A_S_READY0 + buf], (g >> 1) & 1, abort_flag) && mbar_wait(&bars[A_DP_READY], g & 1, abort_flag);
                 if (!ok) break;
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 2);
                 tc_fence_after();
                 const bool masked = kh >= 2 * wk.qt;  // the half reaches the diagonal
                 const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
@@ -385,7 +378,6 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 else dq_half_pass1<false>(sv, gv, scale, 32 * sub, lim, drem, W);
                 float cl = 0.f;  // prefix of g inside the quarter
                 dq_half_local(sv, gv, cl);
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 3);
                 // Every thread has begun this step (and so has read the previous step's slots) once it has arrived at
                 // A_LOADED.  Barriers by step parity, so that a waiter is never two phases away from the phase it names.
                 ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
@@ -409,14 +401,12 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 xg[kq * 128 + r] = c_right;
                 mbar_arrive(&bars[A_X_G0 + 8 * kq + 4 * par + (warp & 3)]);
                 if (half_ok(j)) cc[slot] = c_right;  // for the dk/dv kernel
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 4);
                 // dS goes to columns [0, 64) of the S buffer: every thread has read its scores (A_LOADED, above)
                 dq_half_finish<kF16>(sv, gv, c_edge, packed);
                 tmem_st16(lane_base + kColS + 128 * buf + 16 * kq, packed);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars[A_DS_READY]);
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 5);
             }
             if (!ok) break;
             // epilogue: the quarters store 32 columns of every row each
@@ -686,7 +676,6 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const SmemDesc desc_qmn = make_desc(smem_u32(sQl), kKBox, 1024), desc_domn = make_desc(smem_u32(sDOl), kKBox, 1024);  // MN-major
             const SmemDesc desc_p = make_desc(smem_u32(sP), kKBox, 1024), desc_ds = make_desc(smem_u32(sDS), kKBox, 1024);
             bool ok = true;
-            SB_TRACE_DECL(m);
             auto issue_sdp = [&](uint32_t g, bool last_of_item) {
                 ok = mbar_wait(&bars[B_E_FULL], g & 1, abort_flag);
                 if (!ok) return;
@@ -722,11 +711,9 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             while (ok && have) {
                 const int n = wk.n_qt - wk.kt;
                 for (int j = 0; ok && j < n; ++j, ++g) {
-                    SB_TRACE_EV(m, 0, 1);
                     if (j + 1 < n) {
                         ok = mbar_wait(&bars[B_LOADED], g & 1, abort_flag);
                         if (!ok) break;
-                        SB_TRACE_EV(m, 0, 2);
                         tc_fence_after();
                         issue_sdp(g + 1, j + 2 == n);
                     } else {  // the next item is fetched here, off the path between two items
@@ -735,13 +722,11 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {  // 32 query rows at a time: region i & 1 of the p / ds buffers
                         const int hh = i >> 1, b = i & 1;
-                        SB_TRACE_EV(m, 0, 3 + 2 * hh);
                         ok = mbar_wait(&bars[B_PDS_READY0 + b], hh, abort_flag);  // a region is used twice per step
                         if (ok && b == 0) ok = mbar_wait(&bars[B_L_FULL0 + hh], g & 1, abort_flag);
                         if (ok && j == 0 && i == 0)  // the previous item's accumulators must have been read out
                             ok = mbar_wait(&bars[B_DKV_FREE], (items & 1) ^ 1, abort_flag);
                         if (!ok) break;
-                        SB_TRACE_EV(m, 0, 4 + 2 * hh);
                         tc_fence_after();
                         const SmemDesc ddo = {desc_domn.lo + hh * (kHalfBytes >> 4), desc_domn.hi};
                         const SmemDesc dq = {desc_qmn.lo + hh * (kHalfBytes >> 4), desc_qmn.hi};
@@ -777,16 +762,13 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         uint8_t* srow = sDS + hf * kKBox + (r & 63) * 128;
         uint32_t G = 0, items = 0;
         bool ok = true;
-        SB_TRACE_DECL(c);
         // dk (even quarters) / dv (odd quarters) are stored when the item's last contractions are complete, half of the
         // head dim per thread; S, dP of the next item's first step are computed meanwhile
         auto store_dkdv = [&](const KvWork& e, uint32_t item) {
             ok = mbar_wait(&bars[B_DKV_READY], item & 1, abort_flag);
             if (!ok) return;
-            if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 6);
             kv_store_rows<D, kF16, kFused>(a, sub == 1, e, r, lane_base + (sub == 0 ? kColDK : kColDV), hf * (D / 64));
             mbar_arrive(&bars[B_DKV_FREE]);
-            if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 7);
         };
         SchedConsumer sched;
         int w;
@@ -831,10 +813,8 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const int i = wk.kt + j;
                 const uint32_t g = G + j;
                 const int qi = i * kBM + r;
-                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 1);
                 ok = mbar_wait(&bars[B_SDP_READY], g & 1, abort_flag);
                 if (!ok) break;
-                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 2);
                 tc_fence_after();
                 const bool masked = i == wk.kt;
                 const int lim = min(kBK, max(0, qi - kh * kBK + a.attend_current));
@@ -850,7 +830,6 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     if (masked) kv_chunk<true, kF16>(s1, d1, scale, 32 * sub, lim, drem, c, W, pp, ps);
                     else kv_chunk<false, kF16>(s1, d1, scale, 32 * sub, lim, drem, c, W, pp, ps);
                 }
-                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 3);
                 if (j + 1 < n) load_scalars(i + 1, W, c, drem_raw);
                 // The 64-row p / ds buffers are two regions of 32 rows, each used by one warp quartet of either row half
                 // in turn (rows 0-31 and 64-95 the first region, 32-63 and 96-127 the second).  A region is free once the
@@ -862,7 +841,6 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 // its own previous use was still pending and mistake the completion before that for the one it wants).
                 ok = mbar_wait(&bars[B_PDS_FREE0 + 2 * (warp & 1) + (hh ^ 1)], (g & 1) ^ (hh ^ 1), abort_flag);
                 if (!ok) break;
-                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 4);
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
                     const int off = ((4 * sub + ch) ^ (r & 7)) << 4;
@@ -871,7 +849,6 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 fence_async_smem();
                 mbar_arrive(&bars[B_PDS_READY0 + (warp & 1)]);
-                if ((r & 63) == 0 && kq == 3) SB_TRACE_EV(c, 1 + hh, 5);
             }
             if (!ok) break;
             store_dkdv(wk, items);
@@ -893,12 +870,16 @@ int launch_bwd_kernels(const SbParams& p, const KArgs& a, cudaStream_t st, const
     if (e != cudaSuccess) return (int)e;
     cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16, kFused>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16, kFused>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (p.bwd_phases != SBATTN_BWD_DKDV)
+    if (p.bwd_phases != SBATTN_BWD_DKDV) {
         tc_bwd_dq_kernel<D, kF16, kFused><<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk128, mv128, mdo, a);
+        count_launch();
+    }
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (p.bwd_phases != SBATTN_BWD_DQ)
+    if (p.bwd_phases != SBATTN_BWD_DQ) {
         tc_bwd_dkdv_kernel<D, kF16, kFused><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, mq64, mdo64, a);
+        count_launch();
+    }
     return (int)cudaGetLastError();
 }
 
@@ -926,7 +907,7 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
 
 }  // namespace
 
-int launch_tensor_bwd_impl(const SbParams& p, const KArgs& a, cudaStream_t st) {
+int launch_tensor_bwd(const SbParams& p, const WsLayout&, const KArgs& a, cudaStream_t st) {
     const bool f16 = p.dtype == SBATTN_F16;
     if (p.head_dim == 128) return f16 ? launch_bwd_t<128, true>(p, a, st) : launch_bwd_t<128, false>(p, a, st);
     return f16 ? launch_bwd_t<64, true>(p, a, st) : launch_bwd_t<64, false>(p, a, st);

@@ -8,24 +8,6 @@ namespace sb {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
-// Optional cycle trace of block 0 (development builds only, -DSB_TRACE): role r appends (tag, clock) pairs to
-// status[1024 + r * 8192 ...]; the status buffer must then be large enough.
-#ifdef SB_TRACE
-#define SB_TRACE_DECL(role) uint32_t trace_n_##role = 0
-#define SB_TRACE_EV(role, roleid, tag)                                                         \
-    do {                                                                                       \
-        if (blockIdx.x == 0 && trace_n_##role < 4000) {                                        \
-            uint32_t* tp = a.status + 1024 + (roleid) * 8192 + 2 * trace_n_##role;             \
-            tp[0] = (tag);                                                                     \
-            tp[1] = (uint32_t)clock64();                                                       \
-            ++trace_n_##role;                                                                  \
-        }                                                                                      \
-    } while (0)
-#else
-#define SB_TRACE_DECL(role)
-#define SB_TRACE_EV(role, roleid, tag)
-#endif
-
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -203,7 +185,5 @@ inline bool aligned_mat(const SbMat& m) {
     if (!m.ptr) return true;
     return ((uintptr_t)m.ptr & 15) == 0 && (m.stride_t & 7) == 0 && (m.stride_h & 7) == 0 && (m.stride_b & 7) == 0;
 }
-
-int launch_tensor_bwd_impl(const SbParams& p, const KArgs& a, cudaStream_t st);
 
 }  // namespace sb

@@ -206,7 +206,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             uint32_t pbuf = 0;   // S buffer of the next P to consume
             uint32_t ks = 0, vs = 0;  // K stage of the next S; running count of V tiles consumed by P V
             bool ok = true;
-            SB_TRACE_DECL(m);
             // S of step j of the current item into the next S buffer of the rotation
             auto issue_s = [&](int j, int n) {
                 const uint32_t st = ks;
@@ -242,11 +241,9 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 for (int j = 0; ok && j < n; ++j) {
                     const uint32_t b = pbuf;
                     pbuf = pbuf == 2 ? 0 : pbuf + 1;
-                    SB_TRACE_EV(m, 0, 1);
                     ok = mbar_wait(&bars[P_READY0 + b], (ph_p >> b) & 1, abort_flag);
                     ph_p ^= 1u << b;
                     if (!ok) break;
-                    SB_TRACE_EV(m, 0, 2);
                     const int st = vs & 1;
                     ++vs;
                     uint32_t& ph_vf = st ? ph_vf1 : ph_vf0;
@@ -267,9 +264,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         else mma_ts<true>(leader, tmem + kColO, a_p + k * 8, dv, k * 2048, idesc_o);
                     }
                     mma_commit(leader, &bars[V_EMPTY0 + st]);
-                    SB_TRACE_EV(m, 0, 3);
                     if (j + 3 < n) issue_s(j + 3, n);
-                    SB_TRACE_EV(m, 0, 4);
                 }
                 if (!ok) break;
                 mma_commit(leader, &bars[O_READY]);
@@ -284,7 +279,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const float scale = a.inv_temp * kLog2e;
         uint32_t ph_o = 0, items = 0;
         bool ok = true;
-        SB_TRACE_DECL(c);
         SchedConsumer sched;
         int w;
         Work wk;
@@ -299,10 +293,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const int kt = wk.qt - j;
                 const uint32_t g = step + j, sb = g % 3;
                 const uint32_t s_base = lane_base + kColS0 + 128 * sb;
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 1);
                 ok = mbar_wait(&bars[S_READY0 + sb], (g / 3) & 1, abort_flag);
                 if (!ok) break;
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 2);
                 tc_fence_after();
                 // sweep the quarter right to left relative to an entering carry of 1
                 uint32_t u[32], packed[16];
@@ -313,7 +305,6 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 if (j == 0) fwd_sweep<true>(u, scale, 32 * kq, lim, run);
                 else fwd_sweep<false>(u, scale, 32 * kq, lim, run);
                 fwd_carries(run, Wl, f);
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 3);
                 // The true entering carry travels along the row as a chain through shared memory: a thread takes it from
                 // the quarter to its right (the rightmost quarter from the leftmost one of the previous tile), multiplies
                 // by its own product and passes it on.  Nobody waits for a quarter to its left, so the quarters settle into
@@ -333,14 +324,12 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 xw[kq * 128 + r] = W;
                 mbar_arrive(&bars[X_W0 + 8 * kq + 4 * (g & 1) + (warp & 3)]);
                 if (kFused && kq == 0 && j + 1 == n) wfin[(items & 1) * 128 + r] = W;  // visible to all once O_READY has completed
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 4);
                 if (cw) cw[carry_slot32(wk.slot_base, wk.qt, 4 * kt + kq) * kTileQ] = Win;  // the carry at the quarter's right edge
                 fwd_finish<kF16>(u, f, Win, packed);
                 tmem_st16(s_base + kColPOff + 16 * kq, packed);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars[P_READY0 + sb]);
-                if (r == 0 && (kq == 3 || kq == 0)) SB_TRACE_EV(c, 1 + (kq == 0), 5);
             }
             if (!ok) break;
             step += n;
@@ -399,11 +388,13 @@ int launch_fwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
         cudaError_t ef = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (ef != cudaSuccess) return (int)ef;
         tc_fwd_kernel<D, kF16, true><<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
+        count_launch();
         return (int)cudaGetLastError();
     }
     cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     tc_fwd_kernel<D, kF16, false><<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
+    count_launch();
     return (int)cudaGetLastError();
 }
 
@@ -429,10 +420,6 @@ int launch_tensor_fwd(const SbParams& p, const WsLayout&, const KArgs& a, cudaSt
     const bool f16 = p.dtype == SBATTN_F16;
     if (p.head_dim == 128) return f16 ? launch_fwd_t<128, true>(p, a, st) : launch_fwd_t<128, false>(p, a, st);
     return f16 ? launch_fwd_t<64, true>(p, a, st) : launch_fwd_t<64, false>(p, a, st);
-}
-
-int launch_tensor_bwd(const SbParams& p, const WsLayout&, const KArgs& a, cudaStream_t st) {
-    return launch_tensor_bwd_impl(p, a, st);
 }
 
 }  // namespace sb

@@ -76,6 +76,7 @@ int launch_weights_t(const SbParams& p, float* w, int64_t sb_, int64_t sh, int64
     weights_kernel<T><<<grid, 32 * kWeightWarps, 0, st>>>(view(p.q), view(p.k), p.cu_seqlens, p.cu_width, p.num_seqs, p.batch,
                                                          p.tokens, p.head_dim, p.attend_current ? 1 : 0, p.inv_temp, w, sb_,
                                                          sh, sm);
+    count_launch();
     return (int)cudaGetLastError();
 }
 

@@ -55,6 +55,11 @@ def check_status(device=None, reset=True):
     return val
 
 
+def launch_count():
+    """Kernels the library has launched in this process so far (sbattn_launch_count)."""
+    return int(_lib.lib().sbattn_launch_count())
+
+
 def _require_cuda(*tensors):
     for t in tensors:
         if not t.is_cuda:

@@ -28,3 +28,25 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Lists the worst measured error per test and tensor, so that the margin to each bar is on record in the log."""
+    try:
+        import util
+    except Exception:  # pragma: no cover
+        return
+    if not util.MARGINS:
+        return
+    worst = {}
+    for test, what, name, err, tol in util.MARGINS:
+        key = (test.split("::", 1)[-1], name)
+        if key not in worst or err / tol > worst[key][0] / worst[key][1]:
+            worst[key] = (err, tol)
+    terminalreporter.write_sep("-", "parity margins: worst max-abs error per test and tensor (bar)")
+    tests = {}
+    for (test, name), (err, tol) in worst.items():
+        tests.setdefault(test, []).append(f"{name} {err:.2e}")
+        tests[test + "::bar"] = tol
+    for test in [t for t in tests if not t.endswith("::bar")]:
+        terminalreporter.write_line(f"{test}: " + ", ".join(tests[test]) + f" (bar {tests[test + '::bar']:g})")

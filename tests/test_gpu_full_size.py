@@ -40,6 +40,25 @@ def f64(*xs):
     return [x.float().numpy().astype(np.float64) for x in xs]
 
 
+def test_benchmark_pack_16384_every_sequence():
+    """Config 2 at its own size: the seeded 16384-token pack of the default benchmark (head_dim 128, bf16, 2 of the 32
+    heads, drem != 0), every sequence of both heads in full against the oracle."""
+    sys.path.insert(0, ROOT)
+    import bench
+    lengths = bench.workload("c2")["lengths"]
+    assert lengths == [2943, 3503, 2192, 1807, 3696, 649, 1594]
+    H, D, T = 2, 128, sum(lengths)
+    q, k, v, do, drem = make(H, T, D, seed=0)
+    it = 1 / math.sqrt(D)
+    got = run(q, k, v, do, drem, lengths, it)
+    start = 0
+    for L in lengths:
+        sl = (slice(None), slice(start, start + L))
+        want = orc.sb_dense_bwd(*f64(q[sl], k[sl], v[sl], do[sl]), f64(drem[sl])[0], it)
+        assert_close(NAMES, [x[sl] for x in got], want, TOL_BF16, f"c2 sequence at {start} len {L}")
+        start += L
+
+
 def test_training_shape_8x4096():
     """Config 3: 8 sequences of 4096 tokens, head_dim 128 (4 of the 32 heads; one sequence checked in full)."""
     lengths = [4096] * 8

@@ -70,3 +70,33 @@ def test_static_forward_rejects_oversized_problem():
     p = _params(q, q, q, cu, 128, 0.125, o, rem, nla)
     assert _lib.lib().sbattn_static_scratch_bytes() == 1 << 20
     assert _lib.lib().sbattn_fwd_static(ctypes.byref(p)) == -7
+
+
+def test_static_forward_leaves_device_memory_untouched():
+    """The property the entry point exists for: once the first call on the device has looked the scratch array up, a
+    call neither takes nor returns device memory.  Free memory as the driver reports it (cudaMemGetInfo, which sees
+    every allocation of the process, whoever made it) is the same before and after the call, and so is what PyTorch's
+    allocator holds, since the outputs were allocated beforehand."""
+    from stickbreaking_attention_b200 import _lib, ops
+    lengths = [200, 312, 129]
+    H, T, D = 4, sum(lengths), 128
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(H, T, D, generator=g).bfloat16().cuda() for _ in range(3))
+    cu = torch.tensor(np.cumsum(lengths), device="cuda", dtype=torch.int32)
+    o = torch.empty_like(q)
+    rem = torch.zeros(H, T, dtype=q.dtype, device="cuda")
+    nla = torch.zeros(H, T, dtype=torch.float32, device="cuda")
+    p = _params(q, k, v, cu, max(lengths), 1 / math.sqrt(D), o, rem, nla)
+    fwd_static = _lib.lib().sbattn_fwd_static
+    _lib.check(fwd_static(ctypes.byref(p)), "first call: looks up the scratch address, loads the kernels")
+    torch.cuda.synchronize()
+    ops.check_status(q.device)
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    _lib.check(fwd_static(ctypes.byref(p)), "second call")
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    assert torch.cuda.memory_reserved() == reserved_before
+    ops.check_status(q.device)
+    assert torch.isfinite(o.float()).all()

@@ -44,10 +44,22 @@ def oracle_varlen(q, k, v, do, drem, lengths, inv_temp, attend_current):
                                  np.float64)
 
 
+MARGINS = []   # (test id, what, tensor, max-abs error, bar): printed by conftest.py at the end of the run
+
+
+def note_margin(what, name, err, tol):
+    """Puts a measured max-abs error on record (the terminal summary lists them all with their bars)."""
+    import os
+    test = os.environ.get("PYTEST_CURRENT_TEST", "").split(" ")[0]
+    MARGINS.append((test, what, name, float(err), float(tol)))
+    print(f"parity {what} {name}: max-abs {float(err):.3e} (bar {tol:g})")
+
+
 def assert_close(names, got, want, tol, what=""):
     for n, g, w in zip(names, got, want):
         assert np.isfinite(g).all(), (what, n, "non-finite output")
         err = np.abs(g - w).max() if g.size else 0.0
+        note_margin(what, n, err, tol)
         assert err <= tol, (what, n, float(err), tol)
 
 
