@@ -42,7 +42,9 @@ def f64(*xs):
 
 def test_benchmark_pack_16384_every_sequence():
     """Config 2 at its own size: the seeded 16384-token pack of the default benchmark (head_dim 128, bf16, 2 of the 32
-    heads, drem != 0), every sequence of both heads in full against the oracle."""
+    heads, drem != 0), every sequence of both heads in full against the oracle.  Gradients reach magnitude 4 ... 5 here,
+    where rounding the exact value to bfloat16 alone costs up to 1.5e-2 of the 2e-2 bar (measured on the oracle's own
+    results: dq 1.3e-2, dv 1.5e-2), so the bar applies to the error beyond the output rounding (see assert_close)."""
     sys.path.insert(0, ROOT)
     import bench
     lengths = bench.workload("c2")["lengths"]
@@ -55,7 +57,7 @@ def test_benchmark_pack_16384_every_sequence():
     for L in lengths:
         sl = (slice(None), slice(start, start + L))
         want = orc.sb_dense_bwd(*f64(q[sl], k[sl], v[sl], do[sl]), f64(drem[sl])[0], it)
-        assert_close(NAMES, [x[sl] for x in got], want, TOL_BF16, f"c2 sequence at {start} len {L}")
+        assert_close(NAMES, [x[sl] for x in got], want, TOL_BF16, f"c2 sequence at {start} len {L}", out_half_ulp=2.0 ** -8)
         start += L
 
 
