@@ -63,6 +63,13 @@ KArgs make_args(const SbParams& p, const WsLayout& L) {
         int64_t g = per_head > 0 ? (40ll << 20) / per_head : 8;
         a.head_group = (int32_t)(g < 1 ? 1 : (g > 8 ? 8 : g));
     }
+    {   // Packs of short sequences: the persistent kernels then overlap the end of one item with the start of the next.
+        // The host knows the average length only (the ends live on the device), which is what decides.
+        const int64_t n_seq = p.batch > 0 ? 1 : (p.num_seqs > 0 ? p.num_seqs : 1);
+        const int64_t avg = (int64_t)p.tokens / n_seq;
+        a.defer_fwd = a.defer_dq = avg <= 1024;
+        a.defer_dkdv = avg <= 192;
+    }
     a.q = view(p.q); a.k = view(p.k); a.v = view(p.v); a.o = view(p.o);
     a.d_o = view(p.d_o); a.dq = view(p.dq); a.dk = view(p.dk); a.dv = view(p.dv);
     a.rem = view(p.rem); a.nla = view(p.neg_log_acc); a.d_rem = view(p.d_rem);

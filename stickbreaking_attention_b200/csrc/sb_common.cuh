@@ -110,6 +110,7 @@ struct KArgs {
     float* drem_eff;        // [heads][drem_rows]: drem + do . v, written by the dq kernel when fused
     int64_t drem_rows;      // batch * tokens (tokens for the packed layout)
     int32_t head_group;     // heads whose work is interleaved (sized so that their K and V stay in L2)
+    int32_t defer_fwd, defer_dq, defer_dkdv;  // tensor-core kernels: store an item's result one step into the next item
     int32_t* sched;         // WsHeader::sched
     float inv_temp;
     MatView q, k, v, o, d_o, dq, dk, dv;

@@ -18,6 +18,7 @@
 // global counter.
 #include "sb_tc_common.cuh"
 
+
 namespace sb {
 
 using namespace sm100;
@@ -34,15 +35,17 @@ constexpr int kKBox = 64 * 128;   // bytes of one TMA box of a 64-row tile
 // fp32x2 instructions, and the four reciprocals cost one MUFU operation: with d_i = 1 + e_i,
 // 1 / d_i = (product of the other three) / (d_0 d_1 d_2 d_3).  The exponent is clamped at 30 so that the product of four
 // stays finite (om = 2^-30 instead of something smaller: no visible difference).
-template <bool kMasked>
+template <bool kMasked, bool kGrouped = true>
 __device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, float scale, int col, int lim, float2& om01,
                                        float2& om23) {
     float2 x01 = __fmul2_rn(make_float2(s0, s1), make_float2(scale, scale));
     float2 x23 = __fmul2_rn(make_float2(s2, s3), make_float2(scale, scale));
-    x01.x = fminf(x01.x, 30.f);
-    x01.y = fminf(x01.y, 30.f);
-    x23.x = fminf(x23.x, 30.f);
-    x23.y = fminf(x23.y, 30.f);
+    if (kGrouped) {
+        x01.x = fminf(x01.x, 30.f);
+        x01.y = fminf(x01.y, 30.f);
+        x23.x = fminf(x23.x, 30.f);
+        x23.y = fminf(x23.y, 30.f);
+    }
     if (kMasked) {
         if (col >= lim) x01.x = -INFINITY;
         if (col + 1 >= lim) x01.y = -INFINITY;
@@ -51,6 +54,11 @@ __device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, f
     }
     const float2 d01 = __fadd2_rn(make_float2(ex2_approx(x01.x), ex2_approx(x01.y)), make_float2(1.f, 1.f));
     const float2 d23 = __fadd2_rn(make_float2(ex2_approx(x23.x), ex2_approx(x23.y)), make_float2(1.f, 1.f));
+    if (!kGrouped) {
+        om01 = make_float2(rcp_approx(d01.x), rcp_approx(d01.y));
+        om23 = make_float2(rcp_approx(d23.x), rcp_approx(d23.y));
+        return;
+    }
     const float2 m = __fmul2_rn(d01, d23);  // (d0 d2, d1 d3)
     const float r = rcp_approx(m.x * m.y);
     const float2 rm = make_float2(r * m.y, r * m.x);  // (1 / (d0 d2), 1 / (d1 d3))
@@ -73,8 +81,8 @@ __device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, f
 //     quarter from the rightmost one of the previous step), adds its total and passes it on.  Nobody waits for a quarter
 //     to its right, so the quarters settle into a stagger and the waits of one overlap with the arithmetic of another.
 //     The prefix through a quarter's right edge is also what the dk/dv kernel enters that quarter with (carry_c).
-// Tensor memory: S in two buffers (S of the next step is computed while this one is worked on; dS overwrites the left
-// half of its S buffer as 16-bit operands), dP in one (released as soon as every thread has copied its values to
+// Tensor memory: S in two buffers (S of the next step is computed while this one is worked on; a thread's dS overwrites
+// the first half of its own 32 score columns as 16-bit operands), dP in one (released as soon as every thread has copied its values to
 // registers), dQ.  Warp 16 loads Q, dO (once per item) and the K tiles (three-stage ring: a K tile is needed for S early
 // and for dQ late), warp 18 the V tiles, warp 17 issues every tcgen05.mma.
 constexpr int kDqThreads = 608;
@@ -92,8 +100,8 @@ __device__ __forceinline__ void dq_half_pass1(uint32_t (&s)[32], uint32_t (&dp)[
 #pragma unroll
     for (int q = 7; q >= 0; --q) {
         float2 om[2];
-        stick4<kMasked>(__uint_as_float(s[4 * q]), __uint_as_float(s[4 * q + 1]), __uint_as_float(s[4 * q + 2]),
-                        __uint_as_float(s[4 * q + 3]), scale, col0 + 4 * q, lim, om[0], om[1]);
+        stick4<kMasked, false>(__uint_as_float(s[4 * q]), __uint_as_float(s[4 * q + 1]), __uint_as_float(s[4 * q + 2]),
+                               __uint_as_float(s[4 * q + 3]), scale, col0 + 4 * q, lim, om[0], om[1]);
 #pragma unroll
         for (int h = 1; h >= 0; --h) {
             const int jj = 2 * q + h;
@@ -133,14 +141,14 @@ __device__ __forceinline__ void dq_half_finish(const uint32_t (&beta)[32], const
 
 // kFused (both backward kernels): d_o is the gradient of out = o + rem * v; separate instantiations, the plain ones stay
 // as they are
-template <int D, bool kF16, bool kFused>
+template <int D, bool kF16, bool kFused, bool kDefer>
 __global__ void __launch_bounds__(kDqThreads, 1)
 tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const KArgs a) {
     constexpr int kBoxes = D / 64;
     constexpr int kQBytes = kBM * D * 2;  // a 128-row tile of Q, dO, K or V
     constexpr int kStep = 128;            // keys per step
-    constexpr uint32_t kColS = 0, kColDP = 256, kColDQ = 384;  // S buffer b at +128*b; dS overwrites columns [0, 64) of its S buffer
+    constexpr uint32_t kColS = 0, kColDP = 256, kColDQ = 384;  // S buffer b at +128*b; dS overwrites 16 of every 32 columns of its S buffer
     constexpr uint32_t kCols = 512;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
@@ -304,7 +312,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                     for (int k = 0; k < kStep / 16; ++k) {
                         if (k == 0) mma_ts_dyn(leader, tmem + kColDQ, a_ds, dkmn, 0, idesc_dq, j > 0);
-                        else mma_ts<true>(leader, tmem + kColDQ, a_ds + k * 8, dkmn, k * 2048, idesc_dq);
+                        else mma_ts<true>(leader, tmem + kColDQ, a_ds + (k >> 1) * 32 + (k & 1) * 8, dkmn, k * 2048, idesc_dq);
                     }
                     mma_commit(leader, &bars[A_K_EMPTY0 + kst]);
                     if (j + 2 < n) issue_s(g + 2);  // into the buffer whose dS the contraction above reads: in order
@@ -324,6 +332,34 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const float scale = a.inv_temp * kLog2e;
         uint32_t G = 0, items = 0;
         bool ok = true;
+        // With kDefer (chosen by the host for packs of short sequences) a finished item's dq leaves tensor memory one step
+        // late: its last contraction needs a while to complete, and waiting for it at the end of the item idles the row
+        // threads.  They work on the first step of the next item instead (whose S and dP exist already) and store dq then;
+        // the first dQ contraction of the next item waits for A_DQ_FREE, i.e. for this store.
+        struct PendingItem {
+            int b, h;
+            int64_t tok;
+            uint32_t item;
+            bool row_ok;
+        };
+        PendingItem pend{};
+        bool have_pend = false;
+        const auto store_item = [&]() {  // the quarters store 32 columns of every row each
+            ok = mbar_wait(&bars[A_DQ_READY], pend.item & 1, abort_flag);
+            have_pend = false;
+            if (!ok) return;
+            tc_fence_after();
+            if (kq < D / 32) {
+                const int d0 = kq * 32;
+                char* orow = a.dq.ptr + 2 * ((int64_t)pend.b * a.dq.sb + (int64_t)pend.h * a.dq.sh + pend.tok * a.dq.st + d0);
+                uint32_t v[32];
+                tmem_ld32(lane_base + kColDQ + d0, v);
+                tmem_wait_ld();
+                if (pend.row_ok) store_row32<kF16>(orow, v, a.inv_temp);
+            }
+            tc_fence_before();
+            mbar_arrive(&bars[A_DQ_FREE]);
+        };
         SchedConsumer sched;
         int w;
         Work wk;
@@ -372,16 +408,18 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_ld32(lane_base + kColDP + 32 * kq, gv);
                 tmem_wait_ld();
                 tc_fence_before();
-                mbar_arrive(&bars[A_LOADED]);  // dP is free; so are the S columns that dS will overwrite, once all have arrived
+                mbar_arrive(&bars[A_LOADED]);  // dP is free once all have arrived
                 if (j + 1 < n) prefetch_l2(cw + slot + 4 * kTileQ);  // the next step's carry on its way into the L2
                 if (masked) dq_half_pass1<true>(sv, gv, scale, 32 * sub, lim, drem, W);
                 else dq_half_pass1<false>(sv, gv, scale, 32 * sub, lim, drem, W);
                 float cl = 0.f;  // prefix of g inside the quarter
                 dq_half_local(sv, gv, cl);
-                // Every thread has begun this step (and so has read the previous step's slots) once it has arrived at
-                // A_LOADED.  Barriers by step parity, so that a waiter is never two phases away from the phase it names.
-                ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
-                if (!ok) break;
+                // Exchange barriers by step parity, so that a waiter is never two phases away from the phase it names.  A
+                // slot is not overwritten before its reader has read it: a thread writes its slot of step g + 1 only after
+                // it has received the prefix of that step, which has passed through every quarter of step g after this one,
+                // each of which read its left neighbour's slot first (an item's first step begins only after S of that step
+                // exists, which the issuing warp computes after every thread has delivered dS of the previous item's last
+                // step).
                 const uint32_t par = g & 1, ph = (g >> 1) & 1;
                 // The prefix of g travels along the row as a chain: a thread takes the prefix at its left edge from the
                 // quarter to its left (the leftmost one from the rightmost quarter of the previous step), adds its total
@@ -401,31 +439,30 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 xg[kq * 128 + r] = c_right;
                 mbar_arrive(&bars[A_X_G0 + 8 * kq + 4 * par + (warp & 3)]);
                 if (half_ok(j)) cc[slot] = c_right;  // for the dk/dv kernel
-                // dS goes to columns [0, 64) of the S buffer: every thread has read its scores (A_LOADED, above)
+                // dS goes over the first 16 of this thread's own 32 score columns: nobody else reads or writes them, so no
+                // thread waits for another one's loads.  The contraction finds the 16 keys of k-step k at columns
+                // 32 * (k / 2) + 8 * (k % 2).
                 dq_half_finish<kF16>(sv, gv, c_edge, packed);
-                tmem_st16(lane_base + kColS + 128 * buf + 16 * kq, packed);
+                tmem_st16(lane_base + kColS + 128 * buf + 32 * kq, packed);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars[A_DS_READY]);
+                if (kDefer && j == 0 && have_pend) {
+                    store_item();
+                    if (!ok) break;
+                }
             }
             if (!ok) break;
-            // epilogue: the quarters store 32 columns of every row each
-            ok = mbar_wait(&bars[A_DQ_READY], items & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            if (kq < D / 32) {
-                const int d0 = kq * 32;
-                char* orow = a.dq.ptr + 2 * ((int64_t)wk.b * a.dq.sb + (int64_t)wk.h * a.dq.sh + tok * a.dq.st + d0);
-                uint32_t v[32];
-                tmem_ld32(lane_base + kColDQ + d0, v);
-                tmem_wait_ld();
-                if (row_ok) store_row32<kF16>(orow, v, a.inv_temp);
+            pend = PendingItem{wk.b, wk.h, tok, items, row_ok};
+            have_pend = true;
+            if (!kDefer) {
+                store_item();
+                if (!ok) break;
             }
-            tc_fence_before();
-            mbar_arrive(&bars[A_DQ_FREE]);
             G += n;
             ++items;
         }
+        if (kDefer && ok && have_pend) store_item();  // the block's last item
     }
     tc_teardown(abort_flag, a.status, tmem, kCols, 17);
     sched_finish(a.sched + 2);
@@ -514,7 +551,7 @@ __device__ __forceinline__ void kv_chunk(const uint32_t (&s)[32], const uint32_t
 // Not inlined: it runs once per item, and inside the step loop it would only dilute the instruction cache.
 // With the fused remainder dv also receives rem * do of its own row: the direct path of out = o + rem * v.
 template <int D, bool kF16, bool kFused>
-__device__ __noinline__ void kv_store_rows(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr, int chunk0) {
+__device__ __forceinline__ void kv_store_rows_inl(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr, int chunk0) {
     tc_fence_after();
     const MatView m = is_dv ? a.dv : a.dk;
     const float sc = is_dv ? 1.f : a.inv_temp;
@@ -548,8 +585,12 @@ __device__ __noinline__ void kv_store_rows(const KArgs& a, bool is_dv, const KvW
     }
     tc_fence_before();
 }
-
 template <int D, bool kF16, bool kFused>
+__device__ __noinline__ void kv_store_rows(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr, int chunk0) {
+    kv_store_rows_inl<D, kF16, kFused>(a, is_dv, e, r, taddr, chunk0);
+}
+
+template <int D, bool kF16, bool kFused, bool kDefer>
 __global__ void __launch_bounds__(kKvThreads, 1)
 tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -767,12 +808,19 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         auto store_dkdv = [&](const KvWork& e, uint32_t item) {
             ok = mbar_wait(&bars[B_DKV_READY], item & 1, abort_flag);
             if (!ok) return;
-            kv_store_rows<D, kF16, kFused>(a, sub == 1, e, r, lane_base + (sub == 0 ? kColDK : kColDV), hf * (D / 64));
+            if (kDefer) kv_store_rows_inl<D, kF16, kFused>(a, sub == 1, e, r, lane_base + (sub == 0 ? kColDK : kColDV), hf * (D / 64));
+            else kv_store_rows<D, kF16, kFused>(a, sub == 1, e, r, lane_base + (sub == 0 ? kColDK : kColDV), hf * (D / 64));
             mbar_arrive(&bars[B_DKV_FREE]);
         };
         SchedConsumer sched;
         int w;
         KvWork wk;
+        // With kDefer (packs of sequences of one tile) dk, dv of a finished item are stored inside the first step of the next
+        // item: the item's last contractions need a while to complete; the first contraction of the next item waits for
+        // B_DKV_FREE, i.e. for this store
+        KvWork pend{};
+        uint32_t pend_item = 0;
+        bool have_pend = false;
         while (ok && (w = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk)) >= 0) {
             const int n = wk.n_qt - wk.kt;
             const int kh = 2 * wk.kt + hf;
@@ -831,6 +879,13 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     else kv_chunk<false, kF16>(s1, d1, scale, 32 * sub, lim, drem, c, W, pp, ps);
                 }
                 if (j + 1 < n) load_scalars(i + 1, W, c, drem_raw);
+                if (kDefer && j == 0 && have_pend) {
+                    // Here and not after this step's p / ds have been written: the second row half can write only when the
+                    // first half's contraction of this step is complete, and that contraction waits for B_DKV_FREE.
+                    store_dkdv(pend, pend_item);
+                    have_pend = false;
+                    if (!ok) break;
+                }
                 // The 64-row p / ds buffers are two regions of 32 rows, each used by one warp quartet of either row half
                 // in turn (rows 0-31 and 64-95 the first region, 32-63 and 96-127 the second).  A region is free once the
                 // contractions of its previous use are complete: the other half's, of the previous step for half 0 and of
@@ -851,10 +906,18 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 mbar_arrive(&bars[B_PDS_READY0 + (warp & 1)]);
             }
             if (!ok) break;
-            store_dkdv(wk, items);
+            if (kDefer) {
+                pend = wk;
+                pend_item = items;
+                have_pend = true;
+            } else {
+                store_dkdv(wk, items);
+                if (!ok) break;
+            }
             G += n;
             ++items;
         }
+        if (kDefer && ok && have_pend) store_dkdv(pend, pend_item);  // the block's last item
     }
     tc_teardown(abort_flag, a.status, tmem, kCols, 17);
     sched_finish(a.sched + 4);
@@ -864,23 +927,32 @@ template <int D, bool kF16, bool kFused>
 int launch_bwd_kernels(const SbParams& p, const KArgs& a, cudaStream_t st, const CUtensorMap& mq, const CUtensorMap& mk128,
                        const CUtensorMap& mv128, const CUtensorMap& mdo, const CUtensorMap& mq64, const CUtensorMap& mdo64,
                        int smem_a, int smem_b) {
-    cudaError_t e = cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16, kFused>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16, kFused>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_b);
-    if (e != cudaSuccess) return (int)e;
-    cudaFuncSetAttribute(tc_bwd_dq_kernel<D, kF16, kFused>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    cudaFuncSetAttribute(tc_bwd_dkdv_kernel<D, kF16, kFused>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    const auto launch_dq = [&](auto kernel) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
+        if (e != cudaSuccess) return (int)e;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        kernel<<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk128, mv128, mdo, a);
+        count_launch();
+        return (int)cudaGetLastError();
+    };
+    const auto launch_dkdv = [&](auto kernel) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_b);
+        if (e != cudaSuccess) return (int)e;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        kernel<<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, mq64, mdo64, a);
+        count_launch();
+        return (int)cudaGetLastError();
+    };
     if (p.bwd_phases != SBATTN_BWD_DKDV) {
-        tc_bwd_dq_kernel<D, kF16, kFused><<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk128, mv128, mdo, a);
-        count_launch();
+        const int e = a.defer_dq ? launch_dq(tc_bwd_dq_kernel<D, kF16, kFused, true>) : launch_dq(tc_bwd_dq_kernel<D, kF16, kFused, false>);
+        if (e != 0) return e;
     }
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return (int)e;
     if (p.bwd_phases != SBATTN_BWD_DQ) {
-        tc_bwd_dkdv_kernel<D, kF16, kFused><<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, mq64, mdo64, a);
-        count_launch();
+        const int e = a.defer_dkdv ? launch_dkdv(tc_bwd_dkdv_kernel<D, kF16, kFused, true>)
+                                   : launch_dkdv(tc_bwd_dkdv_kernel<D, kF16, kFused, false>);
+        if (e != 0) return e;
     }
-    return (int)cudaGetLastError();
+    return 0;
 }
 
 template <int D, bool kF16>

@@ -36,6 +36,11 @@ constexpr int kBM = 128, kBN = 128;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColO = 384, kColPOff = 64;  // S buffer i at 128*i (i = step mod 3), its P at +64
 constexpr int kKStages = 3, kVStages = 2;
+// Eighths of every 32-key chunk whose exponential is computed on the FMA pipes (ex2_fma2) instead of the special-function
+// unit.  Measured on the 16384-token benchmark pack (forward, one B200): 0 -> 0.4316 ms, 1 -> 0.4342 ms, 2 -> 0.4455 ms.
+// The special-function unit is not what bounds the sweep (it is ~50 % busy), and the polynomial costs five more issue
+// slots per score than ex2.approx, so the share stays at zero; the path is kept for shapes where that changes.
+constexpr int kFmaExpEighths = 0;
 enum FwdBar { Q_FULL, Q_EMPTY, K_FULL0, K_FULL1, K_FULL2, K_EMPTY0, K_EMPTY1, K_EMPTY2, V_FULL0, V_FULL1, V_EMPTY0, V_EMPTY1, S_READY0, S_READY1,
               S_READY2, P_READY0, P_READY1, P_READY2, O_READY, O_FREE, WORK_FULL0, WORK_FULL1, WORK_EMPTY0, WORK_EMPTY1,
               X_W0,  // 32 barriers for the carry chain: [quarter][tile parity][warp & 3]
@@ -59,7 +64,15 @@ __device__ __forceinline__ void fwd_sweep(uint32_t (&s)[32], float scale, int co
         for (int g = 0; g < 4; ++g) {
             const int idx = g * 8 + m;  // two adjacent keys: the scaling is one packed fp32x2 multiply
             const float2 x = __fmul2_rn(make_float2(__uint_as_float(s[idx]), __uint_as_float(s[idx + 1])), make_float2(scale, scale));
-            float e0 = ex2_approx(fminf(x.x, 15.f)), e1 = ex2_approx(fminf(x.y, 15.f));
+            float e0, e1;
+            if (kFmaExpEighths > 0 && g == 3 && (kFmaExpEighths >= 2 || (m & 2))) {  // this share of the exponentials on the FMA pipes
+                const float2 e = ex2_fma2(make_float2(fmaxf(fminf(x.x, 15.f), -125.f), fmaxf(fminf(x.y, 15.f), -125.f)));
+                e0 = e.x;
+                e1 = e.y;
+            } else {
+                e0 = ex2_approx(fminf(x.x, 15.f));
+                e1 = ex2_approx(fminf(x.y, 15.f));
+            }
             if (kMasked && col0 + idx >= lim) e0 = 0.f;
             if (kMasked && col0 + idx + 1 >= lim) e1 = 0.f;
             s[idx] = __float_as_uint(e0 * run[g]);
@@ -88,15 +101,16 @@ __device__ __forceinline__ void fwd_finish(const uint32_t (&s)[32], const float*
 }
 
 // kFused: out = o + rem * v is formed in the epilogue (a separate instantiation: the plain one stays as it is)
-template <int D, bool kF16, bool kFused>
+// kDefer: an item's output is stored after the first step of the next item instead of at the item's end (chosen by the
+// host for packs of short sequences, where the wait for the item's last contraction is a large share of the item)
+template <int D, bool kF16, bool kFused, bool kDefer>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const KArgs a) {
     constexpr int kTileBytes = kBM * D * 2;
     constexpr int kBoxBytes = 128 * 128;  // one TMA box: 128 rows of 64 elements
     constexpr int kBoxes = D / 64;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + kTileBytes;             // kKStages tiles
     uint8_t* sV = sK + kKStages * kTileBytes;  // kVStages tiles
@@ -105,7 +119,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     uint32_t* tmem_slot = (uint32_t*)(ring + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* xw = (float*)(tmem_slot + 4);  // [quarter][128 rows]: carry leaving the quarter its thread has just swept
-    float* wfin = xw + 512;               // [item parity][128 rows]: remainder of the row, for the fused epilogue of both groups
+    float* wfin = xw + 512;               // [item mod 3][128 rows]: remainder of the row, for the fused epilogue (read one item late)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -117,7 +131,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             if (i == WORK_EMPTY0 || i == WORK_EMPTY1) cnt = 514;  // MMA thread, V producer, 512 row threads
             mbar_init(&bars[i], cnt);
         }
-        *abort_flag = 0;
+        *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
         fence_barrier_init();
     }
     if (warp == 17) {
@@ -134,7 +148,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const int n_items = a.hdr->n_items;
-    const int n_work = n_items * a.heads;
+    const int n_work = *abort_flag ? 0 : n_items * a.heads;
 
     if (warp == 16) {
         // ------------------------------------------------------------------ TMA producer: Q and K
@@ -279,6 +293,44 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const float scale = a.inv_temp * kLog2e;
         uint32_t ph_o = 0, items = 0;
         bool ok = true;
+        // With kDefer a finished item's output leaves tensor memory one step late: its last contraction needs a while to
+        // complete, and waiting for it at the end of the item idles the row threads.  They sweep the first tile of the
+        // next item instead (whose scores exist already) and store the output then; the first P V contraction of the next
+        // item waits for O_FREE, i.e. for this store.  It pays for short items only: for long ones the few registers that
+        // carry the pending item through the loop cost more than the wait.
+        struct PendingItem {
+            int b, h, tok, item;
+            bool row_ok;
+        };
+        PendingItem pend{};
+        bool have_pend = false;
+        const auto store_item = [&]() {  // each quarter stores 32 columns of the head dim of every row
+            ok = mbar_wait(&bars[O_READY], ph_o, abort_flag);
+            ph_o ^= 1;
+            have_pend = false;
+            if (!ok) return;
+            tc_fence_after();
+            if (kq < D / 32) {
+                const int d0 = kq * 32;
+                char* orow = a.o.ptr + 2 * ((int64_t)pend.b * a.o.sb + (int64_t)pend.h * a.o.sh + (int64_t)pend.tok * a.o.st + d0);
+                uint32_t v[32];
+                tmem_ld32(lane_base + kColO + d0, v);
+                tmem_wait_ld();
+                if (pend.row_ok) {
+                    if (kFused) {  // out = o + rem * v, rem rounded to the output type first
+                        const float remf = round16<kF16>(wfin[(pend.item % 3) * 128 + r]);
+                        float x[32];
+                        load_row32<kF16>(a.v.ptr + 2 * ((int64_t)pend.b * a.v.sb + (int64_t)pend.h * a.v.sh +
+                                                         (int64_t)pend.tok * a.v.st + d0), x);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(fmaf(remf, x[i], __uint_as_float(v[i])));
+                    }
+                    store_row32<kF16>(orow, v, 1.f);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&bars[O_FREE]);
+        };
         SchedConsumer sched;
         int w;
         Work wk;
@@ -323,41 +375,26 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 W = Win * Wl;
                 xw[kq * 128 + r] = W;
                 mbar_arrive(&bars[X_W0 + 8 * kq + 4 * (g & 1) + (warp & 3)]);
-                if (kFused && kq == 0 && j + 1 == n) wfin[(items & 1) * 128 + r] = W;  // visible to all once O_READY has completed
+                if (kFused && kq == 0 && j + 1 == n) wfin[(items % 3) * 128 + r] = W;  // visible to all once O_READY has completed
                 if (cw) cw[carry_slot32(wk.slot_base, wk.qt, 4 * kt + kq) * kTileQ] = Win;  // the carry at the quarter's right edge
                 fwd_finish<kF16>(u, f, Win, packed);
                 tmem_st16(s_base + kColPOff + 16 * kq, packed);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars[P_READY0 + sb]);
+                if (kDefer && j == 0 && have_pend) {
+                    store_item();
+                    if (!ok) break;
+                }
             }
             if (!ok) break;
             step += n;
-            // epilogue: each quarter stores 32 columns of the head dim of every row
-            ok = mbar_wait(&bars[O_READY], ph_o, abort_flag);
-            ph_o ^= 1;
-            if (!ok) break;
-            tc_fence_after();
-            if (kq < D / 32) {
-                const int d0 = kq * 32;
-                char* orow = a.o.ptr + 2 * ((int64_t)wk.b * a.o.sb + (int64_t)wk.h * a.o.sh + (int64_t)(wk.start + qi) * a.o.st + d0);
-                uint32_t v[32];
-                tmem_ld32(lane_base + kColO + d0, v);
-                tmem_wait_ld();
-                if (row_ok) {
-                    if (kFused) {  // out = o + rem * v, rem rounded to the output type first
-                        const float remf = round16<kF16>(wfin[(items & 1) * 128 + r]);
-                        float x[32];
-                        load_row32<kF16>(a.v.ptr + 2 * ((int64_t)wk.b * a.v.sb + (int64_t)wk.h * a.v.sh +
-                                                         (int64_t)(wk.start + qi) * a.v.st + d0), x);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(fmaf(remf, x[i], __uint_as_float(v[i])));
-                    }
-                    store_row32<kF16>(orow, v, 1.f);
-                }
+            pend = PendingItem{wk.b, wk.h, wk.start + qi, (int)items, row_ok};
+            have_pend = true;
+            if (!kDefer) {
+                store_item();
+                if (!ok) break;
             }
-            tc_fence_before();
-            mbar_arrive(&bars[O_FREE]);
             ++items;
             if (row_ok && kq == 0) {  // this thread swept the leftmost quarter: W is the remainder of the row
                 const int64_t t = wk.start + qi;
@@ -367,6 +404,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 ((float*)a.nla.ptr)[(int64_t)wk.b * a.nla.sb + (int64_t)wk.h * a.nla.sh + t * a.nla.st] = lg2_approx(W);
             }
         }
+        if (kDefer && ok && have_pend) store_item();  // the block's last item
     }
     tc_teardown(abort_flag, a.status, tmem, kTmemCols, 17);
     sched_finish(a.sched + 0);
@@ -384,18 +422,15 @@ int launch_fwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     // Q + three K stages + two V stages; at least 120 KB so that one block owns the SM and its tensor memory
     constexpr int need = (1 + kKStages + kVStages) * kBM * D * 2 + 1024 + 5120;  // tiles, alignment, barriers and exchange slots
     constexpr int smem = need > 120 * 1024 ? need : 120 * 1024;
-    if (a.fused) {
-        cudaError_t ef = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (ef != cudaSuccess) return (int)ef;
-        tc_fwd_kernel<D, kF16, true><<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
+    const auto launch = [&](auto kernel) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        kernel<<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
         count_launch();
         return (int)cudaGetLastError();
-    }
-    cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<D, kF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    tc_fwd_kernel<D, kF16, false><<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
-    count_launch();
-    return (int)cudaGetLastError();
+    };
+    if (a.fused) return a.defer_fwd ? launch(tc_fwd_kernel<D, kF16, true, true>) : launch(tc_fwd_kernel<D, kF16, true, false>);
+    return a.defer_fwd ? launch(tc_fwd_kernel<D, kF16, false, true>) : launch(tc_fwd_kernel<D, kF16, false, false>);
 }
 
 }  // namespace
