@@ -48,7 +48,7 @@ import torch
 #   python bench.py --workload c2 --heads 16 --steps 1 --warmup 1 --skip kernels,e2e,cpu,sustained,c5,short
 # (16 of the 32 heads, so that the capture stays small), scaled to the workload's 32 heads: traffic grows in
 # proportion to the heads, which are independent.
-NCU_TRAFFIC_BYTES = {"c2-varlen-h32-d128-t16384": {"fwd": 618e6, "bwd_dq": 895e6, "bwd_dkdv": 1002e6}}
+NCU_TRAFFIC_BYTES = {"c2-varlen-h32-d128-t16384": {"fwd": 2 * 296.2e6, "bwd_dq": 2 * 433.7e6, "bwd_dkdv": 2 * 488.2e6}}
 
 METRIC = "fwd+bwd TFLOP/s (varlen, bf16)"
 UNIT = "TFLOP/s"
@@ -342,9 +342,10 @@ def run_ours(args, wl):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # keep stdout to the one JSON line: NCCL prints its version banner there at the VERSION level
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # keep stdout to the one JSON line: NCCL prints its version banner there at the VERSION level (and above);
+        # a level somebody asked for explicitly (WARN, INFO ...) is left alone
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            del os.environ["NCCL_DEBUG"]
         dist.init_process_group("nccl", device_id=dev)
     skip = args.skip
     peaks = measured_peaks()

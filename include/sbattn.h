@@ -48,7 +48,7 @@ extern "C" {
 #define SBATTN_F16 2
 
 /* kernel family */
-#define SBATTN_PATH_AUTO 0   /* tensor-core kernels when eligible (bf16/f16, head_dim 64 or 128, aligned), else SIMT */
+#define SBATTN_PATH_AUTO 0   /* tensor-core kernels when eligible (bf16/f16, head_dim 32, 64 or 128, aligned), else SIMT */
 #define SBATTN_PATH_SIMT 1   /* fp32-arithmetic kernels: any dtype, any head_dim <= 128, any strides     */
 #define SBATTN_PATH_TENSOR 2 /* tcgen05 kernels or SBATTN_EUNSUPPORTED / SBATTN_EALIGN                   */
 
@@ -73,7 +73,7 @@ typedef struct SbVec {
  * reference computes next: tests/test_varlen.py:103, tests/test_attn.py:67, benchmarks/varlen.py:53), with rem rounded
  * to the output dtype first, as in that expression.  The backward then takes d_o = gradient of out and d_rem = gradient
  * of the separately returned rem, needs `rem` (the forward's output) and `v`, and returns dv including rem * d_o.
- * Tensor-core path only (16-bit inputs, head_dim 64 or 128): otherwise SBATTN_EUNSUPPORTED. */
+ * Tensor-core path only (16-bit inputs, head_dim 32, 64 or 128): otherwise SBATTN_EUNSUPPORTED. */
 #define SBATTN_FLAG_FUSED_REMAINDER 1
 
 typedef struct SbParams {

@@ -139,8 +139,12 @@ extern "C" int sbattn_fwd(const SbParams* p) {
     cudaStream_t st = (cudaStream_t)p->stream;
     if (launch_prep(*p, L, st) != 0) return SBATTN_ECUDA;
     const KArgs a = make_args(*p, L);
-    const int e = path == 1 ? launch_tensor_fwd(*p, L, a, st) : launch_simt_fwd(*p, L, a, st);
-    return e == 0 ? SBATTN_OK : SBATTN_ECUDA;
+    if (launch_zero_tail_rows(*p, a, st) != 0) return SBATTN_ECUDA;
+    int e = path == 1 ? launch_tensor_fwd(*p, L, a, st) : launch_simt_fwd(*p, L, a, st);
+    // a layout the tensor-map encoder refuses (nothing has been launched yet): the other kernels take any strides
+    if (e == kMapEncodeFailed && p->path == SBATTN_PATH_AUTO && !(p->flags & SBATTN_FLAG_FUSED_REMAINDER))
+        e = launch_simt_fwd(*p, L, a, st);
+    return e == 0 ? SBATTN_OK : (e == kMapEncodeFailed ? SBATTN_EUNSUPPORTED : SBATTN_ECUDA);
 }
 
 extern "C" int sbattn_bwd(const SbParams* p) {
@@ -166,8 +170,10 @@ extern "C" int sbattn_bwd(const SbParams* p) {
     cudaStream_t st = (cudaStream_t)p->stream;
     const KArgs a = make_args(*p, L);
     if (p->bwd_phases == SBATTN_BWD_ALL && launch_zero_tail(*p, a, st) != 0) return SBATTN_ECUDA;
-    const int e = path == 1 ? launch_tensor_bwd(*p, L, a, st) : launch_simt_bwd(*p, L, a, st);
-    return e == 0 ? SBATTN_OK : SBATTN_ECUDA;
+    int e = path == 1 ? launch_tensor_bwd(*p, L, a, st) : launch_simt_bwd(*p, L, a, st);
+    if (e == kMapEncodeFailed && p->path == SBATTN_PATH_AUTO && !(p->flags & SBATTN_FLAG_FUSED_REMAINDER))
+        e = launch_simt_bwd(*p, L, a, st);
+    return e == 0 ? SBATTN_OK : (e == kMapEncodeFailed ? SBATTN_EUNSUPPORTED : SBATTN_ECUDA);
 }
 
 extern "C" int sbattn_attention_weights(const SbParams* p, float* w, int64_t stride_b, int64_t stride_h, int64_t stride_m) {

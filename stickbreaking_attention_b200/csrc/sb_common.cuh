@@ -142,9 +142,12 @@ template <> __device__ inline __half from_f32<__half>(float x) { return __float2
 extern unsigned long long g_launch_count;
 inline void count_launch() { __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED); }
 
-// launchers implemented in the .cu files (each returns a cudaError_t as int)
+// launchers implemented in the .cu files (each returns a cudaError_t as int; the tensor-core launchers return
+// kMapEncodeFailed when a tensor map could not be encoded, before anything has been launched)
+constexpr int kMapEncodeFailed = -1000;
 int launch_prep(const SbParams& p, const WsLayout& L, cudaStream_t st);
 int launch_zero_tail(const SbParams& p, const KArgs& a, cudaStream_t st);
+int launch_zero_tail_rows(const SbParams& p, const KArgs& a, cudaStream_t st);
 int launch_simt_fwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
 int launch_simt_bwd(const SbParams& p, const WsLayout& L, const KArgs& a, cudaStream_t st);
 bool tensor_path_eligible(const SbParams& p, bool backward, int* why);

@@ -127,7 +127,32 @@ __global__ void zero_tail_kernel(const WsHeader* hdr, MatView dq, MatView dk, Ma
     }
 }
 
+// rem and neg_log_acc of tokens that belong to no sequence are zero (what the reference's zero-initialised outputs hold
+// there, sb_varlen_fwd.py:418-419); every other row is written by the forward kernels, so the caller need not clear them.
+template <typename T>
+__global__ void zero_tail_rows_kernel(const WsHeader* hdr, VecView rem, VecView nla, int heads, int tokens) {
+    const int first = hdr->covered_end;
+    const int rows = tokens - first;
+    if (rows <= 0) return;
+    const int64_t total = (int64_t)rows * heads;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int h = (int)(i % heads);
+        const int64_t t = first + i / heads;
+        ((T*)rem.ptr)[h * rem.sh + t * rem.st] = T(0.f);
+        ((float*)nla.ptr)[h * nla.sh + t * nla.st] = 0.f;
+    }
+}
+
 }  // namespace
+
+int launch_zero_tail_rows(const SbParams& p, const KArgs& a, cudaStream_t st) {
+    if (p.batch > 0) return 0;  // the batched layout covers every token
+    if (p.dtype == SBATTN_F32) zero_tail_rows_kernel<float><<<16, 256, 0, st>>>(a.hdr, a.rem, a.nla, p.heads, p.tokens);
+    else if (p.dtype == SBATTN_F16) zero_tail_rows_kernel<__half><<<16, 256, 0, st>>>(a.hdr, a.rem, a.nla, p.heads, p.tokens);
+    else zero_tail_rows_kernel<__nv_bfloat16><<<16, 256, 0, st>>>(a.hdr, a.rem, a.nla, p.heads, p.tokens);
+    count_launch();
+    return (int)cudaGetLastError();
+}
 
 int launch_zero_tail(const SbParams& p, const KArgs& a, cudaStream_t st) {
     if (p.batch > 0) return 0;  // the batched layout covers every token

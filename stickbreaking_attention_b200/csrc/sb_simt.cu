@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1) simt_fwd_kernel(const KArgs a) {
         gemm_nt(Ss, Qs, Ks, DPP, D);
         __syncthreads();
         // element-wise part: 4 threads per row, 16 keys each
-        if (cw && rp.part == 0) cw[carry_slot(c.slot_base, c.qt, kh) * kTileQ + rloc] = W;
+        if (cw && rp.part == 0) cw[carry_slot(c.slot_base, c.qt, kh) * kTileQ + rloc] = W;  // right edge of the half
         float beta[16], r[16];
         float prod = 1.f;
 #pragma unroll
@@ -230,6 +230,9 @@ __global__ void __launch_bounds__(kThreads, 1) simt_fwd_kernel(const KArgs a) {
             prod *= r[jj];
         }
         const float win = W * quad_right_prod(prod, rp.part);
+        // the carry in the middle of the half as well: a tensor-core backward may follow this forward (the two are
+        // chosen independently, by the alignment of their own operands), and it enters every 32-key quarter directly
+        if (cw && rp.part == 1) cw[carry_slot32(c.slot_base, c.qt, 2 * kh) * kTileQ + rloc] = win;
         float run = win;
 #pragma unroll
         for (int jj = 15; jj >= 0; --jj) {

@@ -1,4 +1,5 @@
-// Tensor-core backward (sm_100a) for bf16 / f16 inputs with head_dim 64 or 128: two kernels, no atomics and no
+// Tensor-core backward (sm_100a) for bf16 / f16 inputs with head_dim 32, 64 or 128 (32 runs on the
+// 64-column kernels: TMA pads the tiles with zeros and the second half of the columns is not stored): two kernels, no atomics and no
 // locks on dq, dk, dv (the reference accumulates dk/dv tiles in global memory under a spin lock,
 // stickbreaking_attention/sb_varlen/sb_varlen_bwd.py:11-53,454-465).
 //
@@ -354,8 +355,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 char* orow = a.dq.ptr + 2 * ((int64_t)pend.b * a.dq.sb + (int64_t)pend.h * a.dq.sh + pend.tok * a.dq.st + d0);
                 uint32_t v[32];
                 tmem_ld32(lane_base + kColDQ + d0, v);
-                tmem_wait_ld();
-                if (pend.row_ok) store_row32<kF16>(orow, v, a.inv_temp);
+                tmem_wait_ld(v);
+                if (pend.row_ok && (D == 128 || a.head_dim > d0)) store_row32<kF16>(orow, v, a.inv_temp);  // D == 64 serves head dim 32 too
             }
             tc_fence_before();
             mbar_arrive(&bars[A_DQ_FREE]);
@@ -381,6 +382,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll 1
                 for (int cidx = 0; cidx < D / 32; ++cidx) {
                     float x[32], y[32];
+                    if (D == 64 && a.head_dim <= 32 * cidx) break;  // D == 64 serves head dim 32 as well
                     load_row32<kF16>(dorow + cidx * 64, x);
                     load_row32<kF16>(vrow + cidx * 64, y);
 #pragma unroll
@@ -406,20 +408,22 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 uint32_t sv[32], gv[32], packed[16];
                 tmem_ld32(lane_base + kColS + 128 * buf + 32 * kq, sv);
                 tmem_ld32(lane_base + kColDP + 32 * kq, gv);
-                tmem_wait_ld();
+                tmem_wait_ld(sv, gv);
                 tc_fence_before();
-                mbar_arrive(&bars[A_LOADED]);  // dP is free once all have arrived
+                mbar_arrive(&bars[A_LOADED]);  // dP is free once all have arrived; see the wait below
                 if (j + 1 < n) prefetch_l2(cw + slot + 4 * kTileQ);  // the next step's carry on its way into the L2
                 if (masked) dq_half_pass1<true>(sv, gv, scale, 32 * sub, lim, drem, W);
                 else dq_half_pass1<false>(sv, gv, scale, 32 * sub, lim, drem, W);
                 float cl = 0.f;  // prefix of g inside the quarter
                 dq_half_local(sv, gv, cl);
-                // Exchange barriers by step parity, so that a waiter is never two phases away from the phase it names.  A
-                // slot is not overwritten before its reader has read it: a thread writes its slot of step g + 1 only after
-                // it has received the prefix of that step, which has passed through every quarter of step g after this one,
-                // each of which read its left neighbour's slot first (an item's first step begins only after S of that step
-                // exists, which the issuing warp computes after every thread has delivered dS of the previous item's last
-                // step).
+                // Every thread has begun this step once it has arrived at A_LOADED.  The wait keeps the row threads within one
+                // step of each other: the four warps of 32 rows exchange prefixes among themselves only, and without it one
+                // such quartet could finish the next step (dP of which is computed as soon as everybody has loaded this one)
+                // and complete this step's phase of A_DS_READY with its arrivals before another quartet has written its dS
+                // (seen as garbage in dq of 32 rows, now and then).  It also keeps the exchange slots and barriers safe across
+                // items.  Barriers by step parity, so that a waiter is never two phases away from the phase it names.
+                ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
+                if (!ok) break;
                 const uint32_t par = g & 1, ph = (g >> 1) & 1;
                 // The prefix of g travels along the row as a chain: a thread takes the prefix at its left edge from the
                 // quarter to its left (the leftmost one from the rightmost quarter of the previous step), adds its total
@@ -439,9 +443,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 xg[kq * 128 + r] = c_right;
                 mbar_arrive(&bars[A_X_G0 + 8 * kq + 4 * par + (warp & 3)]);
                 if (half_ok(j)) cc[slot] = c_right;  // for the dk/dv kernel
-                // dS goes over the first 16 of this thread's own 32 score columns: nobody else reads or writes them, so no
-                // thread waits for another one's loads.  The contraction finds the 16 keys of k-step k at columns
-                // 32 * (k / 2) + 8 * (k % 2).
+                // dS goes over the first 16 of this thread's own 32 score columns, which nobody else reads or writes.  The
+                // contraction finds the 16 keys of k-step k at columns 32 * (k / 2) + 8 * (k % 2).
                 dq_half_finish<kF16>(sv, gv, c_edge, packed);
                 tmem_st16(lane_base + kColS + 128 * buf + 32 * kq, packed);
                 tmem_wait_st();
@@ -551,7 +554,8 @@ __device__ __forceinline__ void kv_chunk(const uint32_t (&s)[32], const uint32_t
 // Not inlined: it runs once per item, and inside the step loop it would only dilute the instruction cache.
 // With the fused remainder dv also receives rem * do of its own row: the direct path of out = o + rem * v.
 template <int D, bool kF16, bool kFused>
-__device__ __forceinline__ void kv_store_rows_inl(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr, int chunk0) {
+__device__ __forceinline__ void kv_store_rows_inl(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr, int chunk0,
+                                                  int n_chunks) {
     tc_fence_after();
     const MatView m = is_dv ? a.dv : a.dk;
     const float sc = is_dv ? 1.f : a.inv_temp;
@@ -570,8 +574,8 @@ __device__ __forceinline__ void kv_store_rows_inl(const KArgs& a, bool is_dv, co
         const int cidx = chunk0 + cc;
         uint32_t v[32];
         tmem_ld32(taddr + cidx * 32, v);
-        tmem_wait_ld();
-        if (key_ok) {
+        tmem_wait_ld(v);
+        if (key_ok && (D == 128 || cc < n_chunks)) {  // D == 64 serves head dim 32 as well: then fewer chunks exist
             if (kFused && add) {
                 float x[32];
                 load_row32<kF16>(add + cidx * 64, x);
@@ -586,8 +590,8 @@ __device__ __forceinline__ void kv_store_rows_inl(const KArgs& a, bool is_dv, co
     tc_fence_before();
 }
 template <int D, bool kF16, bool kFused>
-__device__ __noinline__ void kv_store_rows(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr, int chunk0) {
-    kv_store_rows_inl<D, kF16, kFused>(a, is_dv, e, r, taddr, chunk0);
+__device__ __noinline__ void kv_store_rows(const KArgs& a, bool is_dv, const KvWork e, int r, uint32_t taddr, int chunk0, int n_chunks) {
+    kv_store_rows_inl<D, kF16, kFused>(a, is_dv, e, r, taddr, chunk0, n_chunks);
 }
 
 template <int D, bool kF16, bool kFused, bool kDefer>
@@ -805,11 +809,14 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         bool ok = true;
         // dk (even quarters) / dv (odd quarters) are stored when the item's last contractions are complete, half of the
         // head dim per thread; S, dP of the next item's first step are computed meanwhile
+        // 32-column chunks of the head dim this thread stores: D / 64 of them from chunk hf * (D / 64) on; none for the
+        // second half of the columns when D == 64 serves head dim 32
+        const int kv_chunks = max(0, min(D / 64, a.head_dim / 32 - hf * (D / 64)));
         auto store_dkdv = [&](const KvWork& e, uint32_t item) {
             ok = mbar_wait(&bars[B_DKV_READY], item & 1, abort_flag);
             if (!ok) return;
-            if (kDefer) kv_store_rows_inl<D, kF16, kFused>(a, sub == 1, e, r, lane_base + (sub == 0 ? kColDK : kColDV), hf * (D / 64));
-            else kv_store_rows<D, kF16, kFused>(a, sub == 1, e, r, lane_base + (sub == 0 ? kColDK : kColDV), hf * (D / 64));
+            if (kDefer) kv_store_rows_inl<D, kF16, kFused>(a, sub == 1, e, r, lane_base + (sub == 0 ? kColDK : kColDV), hf * (D / 64), kv_chunks);
+            else kv_store_rows<D, kF16, kFused>(a, sub == 1, e, r, lane_base + (sub == 0 ? kColDK : kColDV), hf * (D / 64), kv_chunks);
             mbar_arrive(&bars[B_DKV_FREE]);
         };
         SchedConsumer sched;
@@ -871,7 +878,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     uint32_t s1[32], d1[32];
                     tmem_ld32(lane_base + kColS + 32 * kq, s1);
                     tmem_ld32(lane_base + kColDP + 32 * kq, d1);
-                    tmem_wait_ld();
+                    tmem_wait_ld(s1, d1);
                     tc_fence_before();
                     mbar_arrive(&bars[B_LOADED]);  // S and dP of this step are free
                     const float drem = drem_value(drem_raw);
@@ -928,17 +935,15 @@ int launch_bwd_kernels(const SbParams& p, const KArgs& a, cudaStream_t st, const
                        const CUtensorMap& mv128, const CUtensorMap& mdo, const CUtensorMap& mq64, const CUtensorMap& mdo64,
                        int smem_a, int smem_b) {
     const auto launch_dq = [&](auto kernel) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a);
-        if (e != cudaSuccess) return (int)e;
-        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        const int e = ensure_kernel_attrs((const void*)kernel, smem_a, true);
+        if (e != 0) return e;
         kernel<<<sm_count(), kDqThreads, smem_a, st>>>(mq, mk128, mv128, mdo, a);
         count_launch();
         return (int)cudaGetLastError();
     };
     const auto launch_dkdv = [&](auto kernel) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_b);
-        if (e != cudaSuccess) return (int)e;
-        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        const int e = ensure_kernel_attrs((const void*)kernel, smem_b, true);
+        if (e != 0) return e;
         kernel<<<sm_count(), kKvThreads, smem_b, st>>>(mq, mk128, mv128, mdo, mq64, mdo64, a);
         count_launch();
         return (int)cudaGetLastError();
@@ -961,13 +966,14 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
     CUtensorMap mq, mdo, mk128, mv128, mq64, mdo64;
     const int kind = kF16 ? 2 : 0;
     const int64_t B = p.batch > 0 ? p.batch : 1;
-    if (encode_tile_map(&mq, p.q.ptr, kind, D, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBM) ||
-        encode_tile_map(&mdo, p.d_o.ptr, kind, D, p.tokens, p.heads, B, p.d_o.stride_t, p.d_o.stride_h, p.d_o.stride_b, kBM) ||
-        encode_tile_map(&mk128, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBM) ||
-        encode_tile_map(&mv128, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBM) ||
-        encode_tile_map(&mq64, p.q.ptr, kind, D, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBK) ||
-        encode_tile_map(&mdo64, p.d_o.ptr, kind, D, p.tokens, p.heads, B, p.d_o.stride_t, p.d_o.stride_h, p.d_o.stride_b, kBK))
-        return 1;
+    const int hd = p.head_dim;  // the maps carry the true head dim; TMA fills the columns up to D with zeros
+    if (encode_tile_map(&mq, p.q.ptr, kind, hd, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBM) ||
+        encode_tile_map(&mdo, p.d_o.ptr, kind, hd, p.tokens, p.heads, B, p.d_o.stride_t, p.d_o.stride_h, p.d_o.stride_b, kBM) ||
+        encode_tile_map(&mk128, p.k.ptr, kind, hd, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBM) ||
+        encode_tile_map(&mv128, p.v.ptr, kind, hd, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBM) ||
+        encode_tile_map(&mq64, p.q.ptr, kind, hd, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBK) ||
+        encode_tile_map(&mdo64, p.d_o.ptr, kind, hd, p.tokens, p.heads, B, p.d_o.stride_t, p.d_o.stride_h, p.d_o.stride_b, kBK))
+        return kMapEncodeFailed;
     // dq kernel: q, do, three k stages, two v stages; dk/dv kernel: k, v, early q / do, late q / do, p, ds, scalars
     constexpr int need = 2 * kBM * D * 2 + (kDqKStages + kDqVStages) * kBM * D * 2 + 3072;
     constexpr int need_b = 6 * kBM * D * 2 + 2 * 2 * 64 * 128 + 3072;
@@ -981,7 +987,7 @@ int launch_bwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
 
 int launch_tensor_bwd(const SbParams& p, const WsLayout&, const KArgs& a, cudaStream_t st) {
     const bool f16 = p.dtype == SBATTN_F16;
-    if (p.head_dim == 128) return f16 ? launch_bwd_t<128, true>(p, a, st) : launch_bwd_t<128, false>(p, a, st);
+    if (p.head_dim > 64) return f16 ? launch_bwd_t<128, true>(p, a, st) : launch_bwd_t<128, false>(p, a, st);
     return f16 ? launch_bwd_t<64, true>(p, a, st) : launch_bwd_t<64, false>(p, a, st);
 }
 

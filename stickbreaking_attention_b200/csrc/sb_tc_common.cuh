@@ -1,6 +1,9 @@
 // Helpers shared by the tensor-core forward and backward kernels.
 #pragma once
 
+#include <mutex>
+#include <unordered_map>
+
 #include "sb_common.cuh"
 #include "sb_sm100.cuh"
 
@@ -200,6 +203,29 @@ inline int sm_count() {
         cache[dev] = n;
     }
     return cache[dev];
+}
+
+// Dynamic shared memory size (and the carve-out preference) of a kernel, set once per kernel and device instead of on
+// every launch: the two driver calls cost more than the launch itself for small problems.
+inline int ensure_kernel_attrs(const void* kernel, int smem_bytes, bool prefer_shared) {
+    static std::mutex mu;
+    static std::unordered_map<const void*, uint64_t> done;  // bit d: set on device d
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return (int)cudaErrorInvalidDevice;
+    const bool tracked = dev >= 0 && dev < 64;
+    if (tracked) {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = done.find(kernel);
+        if (it != done.end() && ((it->second >> dev) & 1)) return 0;
+    }
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return (int)e;
+    if (prefer_shared) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (tracked) {
+        std::lock_guard<std::mutex> lock(mu);
+        done[kernel] |= 1ull << dev;
+    }
+    return 0;
 }
 
 inline bool aligned_mat(const SbMat& m) {

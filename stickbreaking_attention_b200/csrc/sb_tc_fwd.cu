@@ -1,5 +1,5 @@
 // Tensor-core forward (sm_100a): o, rem, neg_log_acc and the carries of W at every 32-key boundary for bf16 / f16 inputs
-// with head_dim 64 or 128.
+// with head_dim 32, 64 or 128 (32 runs on the 64-column kernels; TMA pads the tiles with zeros).
 //
 // One work item = (head, sequence, 128-row query tile); one persistent thread block per SM draws items from a global
 // counter (heaviest first, interleaved over small groups of heads so that their K and V stay in L2).  Per item the key
@@ -315,8 +315,8 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 char* orow = a.o.ptr + 2 * ((int64_t)pend.b * a.o.sb + (int64_t)pend.h * a.o.sh + (int64_t)pend.tok * a.o.st + d0);
                 uint32_t v[32];
                 tmem_ld32(lane_base + kColO + d0, v);
-                tmem_wait_ld();
-                if (pend.row_ok) {
+                tmem_wait_ld(v);
+                if (pend.row_ok && (D == 128 || a.head_dim > d0)) {  // D == 64 serves head dim 32 as well
                     if (kFused) {  // out = o + rem * v, rem rounded to the output type first
                         const float remf = round16<kF16>(wfin[(pend.item % 3) * 128 + r]);
                         float x[32];
@@ -353,7 +353,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 float run[4], f[4];
                 float Wl = 1.f;
                 tmem_ld32(s_base + 32 * kq, u);
-                tmem_wait_ld();
+                tmem_wait_ld(u);
                 if (j == 0) fwd_sweep<true>(u, scale, 32 * kq, lim, run);
                 else fwd_sweep<false>(u, scale, 32 * kq, lim, run);
                 fwd_carries(run, Wl, f);
@@ -412,19 +412,21 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
 template <int D, bool kF16>
 int launch_fwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
+    // D is the padded head dim (64 or 128); the tensor maps carry the true one, and TMA fills the columns beyond it with zeros
     CUtensorMap mq, mk, mv;
     const int kind = kF16 ? 2 : 0;
     const int64_t B = p.batch > 0 ? p.batch : 1;
-    if (encode_tile_map(&mq, p.q.ptr, kind, D, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBM) ||
-        encode_tile_map(&mk, p.k.ptr, kind, D, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBN) ||
-        encode_tile_map(&mv, p.v.ptr, kind, D, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBN))
-        return 1;
+    const int hd = p.head_dim;
+    if (encode_tile_map(&mq, p.q.ptr, kind, hd, p.tokens, p.heads, B, p.q.stride_t, p.q.stride_h, p.q.stride_b, kBM) ||
+        encode_tile_map(&mk, p.k.ptr, kind, hd, p.tokens, p.heads, B, p.k.stride_t, p.k.stride_h, p.k.stride_b, kBN) ||
+        encode_tile_map(&mv, p.v.ptr, kind, hd, p.tokens, p.heads, B, p.v.stride_t, p.v.stride_h, p.v.stride_b, kBN))
+        return kMapEncodeFailed;
     // Q + three K stages + two V stages; at least 120 KB so that one block owns the SM and its tensor memory
     constexpr int need = (1 + kKStages + kVStages) * kBM * D * 2 + 1024 + 5120;  // tiles, alignment, barriers and exchange slots
     constexpr int smem = need > 120 * 1024 ? need : 120 * 1024;
     const auto launch = [&](auto kernel) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
+        const int e = ensure_kernel_attrs((const void*)kernel, smem, false);
+        if (e != 0) return e;
         kernel<<<sm_count(), kFwdThreads, smem, st>>>(mq, mk, mv, a);
         count_launch();
         return (int)cudaGetLastError();
@@ -438,22 +440,26 @@ int launch_fwd_t(const SbParams& p, const KArgs& a, cudaStream_t st) {
 bool tensor_path_eligible(const SbParams& p, bool backward, int* why) {
     *why = SBATTN_EUNSUPPORTED;
     if (p.dtype != SBATTN_BF16 && p.dtype != SBATTN_F16) return false;
-    if (p.head_dim != 64 && p.head_dim != 128) return false;
+    // head dim 32 runs on the 64-column kernels: TMA pads the tiles with zeros, the epilogues skip the second 32-column chunk
+    if (p.head_dim != 32 && p.head_dim != 64 && p.head_dim != 128) return false;
     *why = SBATTN_EALIGN;
-    if (!aligned_mat(p.q) || !aligned_mat(p.k) || !aligned_mat(p.v)) return false;
+    const auto ok = [&](const SbMat& m) {
+        // outer strides of at least a row: a broadcast head (stride 0) is not something a tensor map can describe
+        return aligned_mat(m) && m.stride_t >= p.head_dim && (p.heads <= 1 || m.stride_h >= p.head_dim) &&
+               (p.batch <= 1 || m.stride_b >= p.head_dim);
+    };
+    if (!ok(p.q) || !ok(p.k) || !ok(p.v)) return false;
     if (backward) {
-        if (!aligned_mat(p.d_o) || !aligned_mat(p.dq) || !aligned_mat(p.dk) || !aligned_mat(p.dv)) return false;
-        if (p.d_o.stride_t < p.head_dim) return false;
-    } else if (!aligned_mat(p.o)) {
+        if (!ok(p.d_o) || !ok(p.dq) || !ok(p.dk) || !ok(p.dv)) return false;
+    } else if (!ok(p.o)) {
         return false;
     }
-    if (p.q.stride_t < p.head_dim || p.k.stride_t < p.head_dim || p.v.stride_t < p.head_dim) return false;
     return true;
 }
 
 int launch_tensor_fwd(const SbParams& p, const WsLayout&, const KArgs& a, cudaStream_t st) {
     const bool f16 = p.dtype == SBATTN_F16;
-    if (p.head_dim == 128) return f16 ? launch_fwd_t<128, true>(p, a, st) : launch_fwd_t<128, false>(p, a, st);
+    if (p.head_dim > 64) return f16 ? launch_fwd_t<128, true>(p, a, st) : launch_fwd_t<128, false>(p, a, st);
     return f16 ? launch_fwd_t<64, true>(p, a, st) : launch_fwd_t<64, false>(p, a, st);
 }
 

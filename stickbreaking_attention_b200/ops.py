@@ -261,8 +261,10 @@ def _forward(q, k, v, batched, cu_seqlens, max_seqlens, logit_scale, attend_curr
         _require_cuda(q, k, v)
     q, k, v = _unit_inner(q), _unit_inner(k), _unit_inner(v)
     o = _empty_like_rows(q)
-    rem = torch.zeros(q.shape[:-1], dtype=q.dtype, device=q.device)
-    neg_log_acc = torch.zeros(q.shape[:-1], dtype=torch.float32, device=q.device)
+    # no zero-fill: the library writes every row of rem and neg_log_acc (zeros for tokens outside every sequence, which is
+    # what the reference's zero-initialised outputs hold there, sb_varlen_fwd.py:418-419)
+    rem = torch.empty(q.shape[:-1], dtype=q.dtype, device=q.device)
+    neg_log_acc = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
     if batched:
         n_seqs, heads, tokens = q.size(0), q.size(1), q.size(2)
     else:
@@ -292,6 +294,8 @@ def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale
     q, k, v, do = _unit_inner(q), _unit_inner(k), _unit_inner(v), _unit_inner(do)
     if do.dtype != q.dtype:
         do = do.to(q.dtype)
+    if fused and not compiling and not _tma_ok(do):
+        do = do.contiguous().clone()  # the fused backward exists in the tensor-core kernels only: give them an aligned copy
     if dr.dtype != q.dtype:
         dr = dr.to(q.dtype)
     if out is not None:
@@ -320,14 +324,21 @@ def _backward(do, dr, q, k, v, batched, cu_seqlens, max_seqlens, ws, logit_scale
     return dq, dk, dv
 
 
-def fusable(q):
-    """Whether the fused remainder (out = o + rem * v inside the kernels) is available for tensors like q: it exists in
-    the tensor-core kernels only."""
-    if not (q.dtype in (torch.bfloat16, torch.float16) and q.size(-1) in (64, 128) and _forced_path != "simt"
-            and all(st % 8 == 0 for st in q.stride()[:-1])):
+def _tma_ok(t):
+    """Whether the tensor-core kernels can read or write t: 16-byte aligned base, outer strides that are multiples of
+    8 elements and at least one row long (a broadcast head has stride 0).  Addresses are not visible while a program is
+    being traced: a misaligned tensor then fails in the operator."""
+    if t.stride(-1) != 1 or not all(st % 8 == 0 and (st >= t.size(-1) or n == 1) for st, n in zip(t.stride()[:-1], t.shape[:-1])):
         return False
-    # addresses are not visible while a program is being traced: a misaligned tensor then fails in the operator
-    return torch.compiler.is_compiling() or q.data_ptr() % 16 == 0
+    return torch.compiler.is_compiling() or t.data_ptr() % 16 == 0
+
+
+def fusable(q, k=None, v=None):
+    """Whether the fused remainder (out = o + rem * v inside the kernels) is available for these tensors: it exists in
+    the tensor-core kernels only, which need 16-bit inputs, a head_dim they take and operands TMA can read."""
+    if not (q.dtype in (torch.bfloat16, torch.float16) and q.size(-1) in (32, 64, 128) and _forced_path != "simt"):
+        return False
+    return all(_tma_ok(t) for t in (q, k, v) if t is not None)
 
 
 def attention_weights(q, k, cu_seqlens=None, logit_scale=None, attend_current=False):

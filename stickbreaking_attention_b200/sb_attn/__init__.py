@@ -37,7 +37,7 @@ def sb_attn(q, k, v, inv_temp=None, zero_start=True, attend_current=False, fuse_
     ``fuse_remainder=True`` (no counterpart in the reference) returns ``o + rem[..., None] * v`` as the first result."""
     if inv_temp is None:
         inv_temp = 1 / math.sqrt(q.size(-1))
-    if fuse_remainder and not fusable(q):  # fp32-arithmetic kernels: the same sum, formed here
+    if fuse_remainder and not fusable(q, k, v):  # fp32-arithmetic kernels: the same sum, formed here
         o, rem = sb_attn_(q, k, v, inv_temp, attend_current=attend_current)
         return o + rem[..., None] * v, rem
     return sb_attn_(q, k, v, inv_temp, attend_current=attend_current, fuse_remainder=fuse_remainder)

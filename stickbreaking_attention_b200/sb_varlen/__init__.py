@@ -48,7 +48,7 @@ def sb_attn_varlen(q, k, v, cu_seqlens, max_seqlens=None, inv_temp=None, zero_st
         cu_seqlens = cu_seqlens[1:]
     if inv_temp is None:
         inv_temp = 1 / math.sqrt(q.size(-1))
-    if fuse_remainder and not fusable(q):  # fp32-arithmetic kernels: the same sum, formed here
+    if fuse_remainder and not fusable(q, k, v):  # fp32-arithmetic kernels: the same sum, formed here
         o, rem = sb_attn_varlen_(q, k, v, inv_temp, cu_seqlens, max_seqlens, attend_current)
         return o + rem[..., None] * v, rem
     return sb_attn_varlen_(q, k, v, inv_temp, cu_seqlens, max_seqlens, attend_current, fuse_remainder)

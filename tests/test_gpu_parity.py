@@ -198,7 +198,7 @@ def test_bad_seqlens_reported_not_faulting():
 
 
 def test_tensor_core_path_is_taken():
-    """Forcing the tcgen05 kernels must succeed for bf16/f16 with head_dim 64/128 and be refused otherwise."""
+    """Forcing the tcgen05 kernels must succeed for bf16/f16 with head_dim 32, 64 or 128 and be refused otherwise."""
     import stickbreaking_attention_b200 as sb
     from stickbreaking_attention_b200 import sb_attn_varlen
     from stickbreaking_attention_b200._lib import SbAttnError
@@ -210,7 +210,7 @@ def test_tensor_core_path_is_taken():
             o, rem = sb_attn_varlen(q, q, q, cu, 300, zero_start=False)
             (o.float().sum() + rem.float().sum()).backward()
             assert torch.isfinite(q.grad.float()).all()
-        q = torch.randn(2, 300, 48, device="cuda", dtype=torch.bfloat16)
+        q = torch.randn(2, 300, 50, device="cuda", dtype=torch.bfloat16)  # rows of 100 bytes: not whole 16-byte units
         with pytest.raises(SbAttnError):
             sb_attn_varlen(q, q, q, cu, 300, zero_start=False)
         q = torch.randn(2, 300, 64, device="cuda", dtype=torch.float32)
@@ -218,6 +218,87 @@ def test_tensor_core_path_is_taken():
             sb_attn_varlen(q, q, q, cu, 300, zero_start=False)
     finally:
         sb.set_path("auto")
+
+
+@pytest.mark.parametrize("D", [32])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_tensor_path_head_dim_32(D, dtype):
+    """Head dim 32 (the reference's test grid has 16 and 32, tests/test_attn.py:42; 16 stays on the fp32 kernels) on the
+    tcgen05 kernels, which work on 64 or 128 columns that TMA pads with zeros: packed layout with ragged sequences,
+    against the oracle; then the batched layout and the fused remainder on the same path."""
+    import stickbreaking_attention_b200 as sb
+    lengths = [1, 130, 257, 64, 300, 127]
+    H, T = 3, sum(lengths)
+    ins = [rounded(x, dtype) for x in synth(H, T, D, seed=40 + D)]
+    it = 1 / math.sqrt(D)
+    sb.set_path("tensor")
+    try:
+        got = run_varlen(*ins, lengths, it, D == 32, dtype)
+        want = oracle_varlen(*ins, lengths, it, D == 32)
+        assert_close(NAMES, got, want, TOL_BF16, f"tensor path D={D}")
+        B, Hb, Tb = 2, 2, 200
+        ins4 = [rounded(x, dtype) for x in synth(B * Hb, Tb, D, seed=41 + D, dist="reftest")]
+        ins4 = [x.reshape((B, Hb) + x.shape[1:]) for x in ins4]
+        got = run_batched(*ins4, it, False, dtype)
+        want = orc.sb_batched_fwd_bwd(*ins4, it, False)
+        assert_close(NAMES, got, want, TOL_BF16, f"tensor path batched D={D}")
+    finally:
+        sb.set_path("auto")
+
+
+def test_broadcast_head_falls_back():
+    """k and v expanded over the heads (stride 0, multi-query attention): a tensor map cannot describe them, so the
+    fp32-arithmetic kernels take the call; same results as with materialised copies."""
+    from stickbreaking_attention_b200 import sb_attn_varlen
+    lengths = [150, 106]
+    H, T, D = 4, 256, 64
+    q, k, v, do, drem = [rounded(x, torch.bfloat16) for x in synth(H, T, D, seed=77)]
+    k[:] = k[:1]
+    v[:] = v[:1]
+    tq = torch.from_numpy(q).cuda().bfloat16()
+    tk1, tv1 = (torch.from_numpy(x[:1]).cuda().bfloat16() for x in (k, v))
+    cu = torch.tensor(np.cumsum(lengths), device="cuda")
+    o, rem = sb_attn_varlen(tq, tk1.expand(H, T, D), tv1.expand(H, T, D), cu, max(lengths), zero_start=False)
+    want = oracle_varlen(q, k, v, do, drem, lengths, 1 / math.sqrt(D), False)
+    got = [x.detach().double().cpu().numpy() for x in (o, rem)]
+    assert_close(("o", "rem"), got, want[:2], TOL_BF16, "broadcast k, v")
+
+
+def test_forward_after_fp32_path_feeds_tensor_backward():
+    """The forward and the backward choose their kernels independently (by the alignment of their own operands): an
+    output buffer the tensor-core forward cannot write sends the forward to the fp32-arithmetic kernels, whose carries the
+    tensor-core backward must be able to use."""
+    from stickbreaking_attention_b200 import ops
+    lengths = [300, 212]
+    H, T, D = 2, 512, 64
+    ins = [rounded(x, torch.bfloat16) for x in synth(H, T, D, seed=91)]
+    q, k, v, do, drem = (torch.from_numpy(x).cuda().bfloat16() for x in ins)
+    cu = torch.tensor(np.cumsum(lengths), dtype=torch.int32, device="cuda")
+    scale = 1 / math.sqrt(D)
+    o = torch.empty(H, T, D + 2, dtype=torch.bfloat16, device="cuda")[..., 2:]  # rows start 4 bytes off a 16-byte boundary
+    rem = torch.empty(H, T, dtype=torch.bfloat16, device="cuda")
+    nla = torch.empty(H, T, dtype=torch.float32, device="cuda")
+    fb, bb = ops.workspace_bytes(False, cu.numel(), H, T, max(lengths))
+    ws = torch.empty(fb, dtype=torch.uint8, device="cuda")
+    ops._forward_into(q, k, v, False, cu, max(lengths), scale, False, False, o, rem, nla, ws)
+    dq, dk, dv = ops.varlen_bwd(do, drem, q, k, v, cu, max(lengths), ws, scale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = oracle_varlen(*ins, lengths, scale, False)
+    got = [x.detach().double().cpu().numpy() for x in (o, rem, dq, dk, dv)]
+    assert_close(NAMES, got, want, TOL_BF16, "fp32-path forward, tensor-core backward")
+
+
+def test_uncovered_tokens_get_zero_remainder():
+    """rem and neg_log_acc of tokens behind the last sequence are zero although the caller's buffers are not cleared."""
+    from stickbreaking_attention_b200 import ops
+    H, T, D = 2, 300, 64
+    q = torch.randn(H, T, D, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([100, 180], dtype=torch.int32, device="cuda")
+    o, rem, nla, _ = ops.varlen_fwd(q, q, q, cu, 100, 0.125, no_grad=True)
+    torch.cuda.synchronize()
+    assert torch.all(rem[:, 180:] == 0) and torch.all(nla[:, 180:] == 0)
+    assert torch.all(rem[:, 0] == 1) and torch.all(rem[:, 100] == 1)
 
 
 def test_empty_and_no_grad():
