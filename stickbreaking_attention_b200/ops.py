@@ -20,6 +20,29 @@ _status_words = {}
 _forced_path = os.environ.get("SBATTN_PATH", "auto")
 
 
+_carry_policy = os.environ.get("SBATTN_CARRIES", "save")
+
+
+def set_carry_policy(name):
+    """What the autograd functions keep between forward and backward.
+
+    'save' (default): the forward's workspace with the per-tile carries, two floats per query row and 64 keys.  That is
+    H * sum(ceil(len / 128) * (ceil(len / 128) + 1)) KiB: 95 MB for the 16384-token benchmark pack of 32 heads, 2 GB for one
+    65536-token sequence of 8 heads; it grows with the square of the sequence length, where the reference keeps 4 bytes per
+    row (its neg_log_acc, sb_varlen/__init__.py:41).
+    'recompute': nothing beyond q, k, v and rem; the backward runs the forward kernel once more to rebuild the carries
+    in scratch memory that lives only for the backward call.  Costs one forward (about a fifth of forward + backward),
+    keeps the memory held between the two passes linear in the sequence length.  Same gradients, bit for bit."""
+    global _carry_policy
+    if name not in ("save", "recompute"):
+        raise ValueError(name)
+    _carry_policy = name
+
+
+def get_carry_policy():
+    return _carry_policy
+
+
 def set_path(name):
     """'auto' (default), 'simt' (fp32-arithmetic kernels) or 'tensor' (tcgen05 kernels or an error)."""
     global _forced_path

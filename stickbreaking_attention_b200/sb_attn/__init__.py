@@ -4,7 +4,7 @@ import math
 
 import torch
 
-from ..ops import attn_bwd, attn_fwd, fusable
+from ..ops import attn_bwd, attn_fwd, fusable, get_carry_policy
 
 
 class StickBreakingAttention(torch.autograd.Function):
@@ -12,9 +12,10 @@ class StickBreakingAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, inv_temp, attend_current=False, fuse_remainder=False):
         no_grad = not any(ctx.needs_input_grad[:3])
-        o, rem, neg_log_acc, workspace = attn_fwd(q, k, v, inv_temp, attend_current=attend_current, no_grad=no_grad,
-                                                  fuse_remainder=fuse_remainder)
-        ctx.save_for_backward(q, k, v, workspace, rem)
+        ctx.recompute = not no_grad and get_carry_policy() == "recompute"  # see ops.set_carry_policy
+        o, rem, neg_log_acc, workspace = attn_fwd(q, k, v, inv_temp, attend_current=attend_current,
+                                                  no_grad=no_grad or ctx.recompute, fuse_remainder=fuse_remainder)
+        ctx.save_for_backward(q, k, v, rem if ctx.recompute else workspace, rem)
         ctx.fuse_remainder = fuse_remainder
         ctx.logit_scale = inv_temp
         ctx.attend_current = attend_current
@@ -23,6 +24,9 @@ class StickBreakingAttention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, drem):
         q, k, v, workspace, rem = ctx.saved_tensors
+        if ctx.recompute:  # rebuild the carries: the forward once more, its o and rem dropped
+            workspace = attn_fwd(q, k, v, ctx.logit_scale, attend_current=ctx.attend_current,
+                                 fuse_remainder=ctx.fuse_remainder)[3]
         if do is None:
             do = torch.zeros_like(q)
         if drem is None:

@@ -4,7 +4,7 @@ import math
 
 import torch
 
-from ..ops import fusable, varlen_bwd, varlen_fwd
+from ..ops import fusable, get_carry_policy, varlen_bwd, varlen_fwd
 
 
 class StickBreakingAttention(torch.autograd.Function):
@@ -13,10 +13,11 @@ class StickBreakingAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, max_seqlens, inv_temp, attend_current, fuse_remainder=False):
         no_grad = not any(ctx.needs_input_grad[:3])
+        ctx.recompute = not no_grad and get_carry_policy() == "recompute"  # see ops.set_carry_policy
         o, rem, neg_log_acc, workspace = varlen_fwd(q, k, v, cu_seqlens, max_seqlens, inv_temp,
-                                                    attend_current=attend_current, no_grad=no_grad,
+                                                    attend_current=attend_current, no_grad=no_grad or ctx.recompute,
                                                     fuse_remainder=fuse_remainder)
-        ctx.save_for_backward(q, k, v, cu_seqlens, workspace, rem)
+        ctx.save_for_backward(q, k, v, cu_seqlens, rem if ctx.recompute else workspace, rem)
         ctx.fuse_remainder = fuse_remainder
         ctx.logit_scale = inv_temp
         ctx.max_seqlens = max_seqlens
@@ -26,6 +27,9 @@ class StickBreakingAttention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, drem):
         q, k, v, cu_seqlens, workspace, rem = ctx.saved_tensors
+        if ctx.recompute:  # rebuild the carries: the forward once more, its o and rem dropped
+            workspace = varlen_fwd(q, k, v, cu_seqlens, ctx.max_seqlens, ctx.logit_scale, attend_current=ctx.attend_current,
+                                   fuse_remainder=ctx.fuse_remainder)[3]
         if do is None:
             do = torch.zeros_like(q)
         if drem is None:

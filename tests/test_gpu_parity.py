@@ -301,6 +301,26 @@ def test_uncovered_tokens_get_zero_remainder():
     assert torch.all(rem[:, 0] == 1) and torch.all(rem[:, 100] == 1)
 
 
+def test_recomputed_carries_give_the_same_gradients():
+    """set_carry_policy('recompute') keeps nothing quadratic in the sequence length between forward and backward;
+    results are the same bits as with saved carries, in both layouts."""
+    import stickbreaking_attention_b200 as sb
+    lengths = [700, 324, 129]
+    H, T, D = 2, sum(lengths), 128
+    ins = [rounded(x, torch.bfloat16) for x in synth(H, T, D, seed=23)]
+    ins4 = [x.reshape((1, H) + x.shape[1:]) for x in ins]
+    want = run_varlen(*ins, lengths, 0.1, False, torch.bfloat16)
+    want4 = run_batched(*ins4, 0.1, True, torch.bfloat16)
+    sb.set_carry_policy("recompute")
+    try:
+        got = run_varlen(*ins, lengths, 0.1, False, torch.bfloat16)
+        got4 = run_batched(*ins4, 0.1, True, torch.bfloat16)
+    finally:
+        sb.set_carry_policy("save")
+    for x, y in zip(want + want4, got + got4):
+        assert np.array_equal(x, y)
+
+
 def test_empty_and_no_grad():
     from stickbreaking_attention_b200 import sb_attn_varlen
     q = torch.randn(2, 0, 64, device="cuda", dtype=torch.bfloat16)
