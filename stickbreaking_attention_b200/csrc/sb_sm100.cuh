@@ -66,6 +66,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // make generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05.mma operand reads)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Rows [first, last) of a swizzled operand tile are set to zero by one warp.  The tile is a series of boxes of 128-byte
+// rows, box_bytes apart; the 128-byte swizzle permutes 16-byte chunks inside a row only, so a row is 128 contiguous bytes
+// of its box.  For the tiles at the ragged end of a sequence: the rows behind the end belong to the next sequence or to
+// nobody, and although they only ever meet zero weights in a contraction, 0 * NaN is NaN.  zero_rows_done() makes the
+// writes of all lanes visible to the tensor core.
+__device__ __forceinline__ void zero_rows(uint8_t* tile, int boxes, int box_bytes, int first, int last, int lane) {
+    for (int bx = 0; bx < boxes; ++bx)
+        for (int i = first * 8 + lane; i < last * 8; i += 32) *(uint4*)(tile + bx * box_bytes + i * 16) = make_uint4(0u, 0u, 0u, 0u);
+}
+// The same for the rows from `first` to the next multiple of 16 (none if `first` is one): four stores per lane and box
+__device__ __forceinline__ void zero_rows_to_16(uint8_t* tile, int boxes, int box_bytes, int first, int lane) {
+    uint8_t* slice = tile + (first >> 4) * 2048;  // 16 rows of 128 bytes
+    for (int bx = 0; bx < boxes; ++bx)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int chunk = lane + 32 * t;  // 16-byte chunk of the slice: row chunk / 8
+            if ((chunk >> 3) >= (first & 15)) *(uint4*)(slice + bx * box_bytes + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+}
+__device__ __forceinline__ void zero_rows_done() {
+    fence_async_smem();
+    __syncwarp();
+}
+// out of line, for kernels whose register allocation is better left alone
+static __device__ __noinline__ void zero_rows_ool(uint8_t* tile, int boxes, int box_bytes, int first, int last, int lane) {
+    zero_rows(tile, boxes, box_bytes, first, last, lane);
+    zero_rows_done();
+}
+
 __device__ __forceinline__ void prefetch_l2(const void* gptr) { asm volatile("prefetch.global.L2 [%0];" ::"l"(gptr)); }
 
 // 4-byte asynchronous copy global -> shared (a prefetched per-row scalar never occupies a register while in flight)

@@ -89,7 +89,8 @@ __device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, f
 constexpr int kDqThreads = 608;
 constexpr int kDqKStages = 3, kDqVStages = 2;
 enum DqBar { A_QDO_FULL, A_QDO_EMPTY, A_K_FULL0, A_K_FULL1, A_K_FULL2, A_K_EMPTY0, A_K_EMPTY1, A_K_EMPTY2, A_V_FULL0, A_V_FULL1,
-             A_V_EMPTY0, A_V_EMPTY1, A_S_READY0, A_S_READY1, A_DP_READY, A_LOADED, A_DS_READY, A_DQ_READY,
+             A_V_EMPTY0, A_V_EMPTY1, A_S_READY0, A_S_READY1, A_DP_READY, A_LOADED, A_DS_READY0, A_DS_READY1, A_DS_READY2, A_DS_READY3,
+             A_DQ_READY,
              A_DQ_FREE, A_WORK_FULL0, A_WORK_FULL1, A_WORK_EMPTY0, A_WORK_EMPTY1,
              A_X_G0,  // 32 barriers for the prefixes: [quarter][step parity][warp & 3]
              kNumDqBars = A_X_G0 + 32 };
@@ -168,7 +169,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         for (int i = 0; i < kNumDqBars; ++i) {
             uint32_t cnt = 1;
             if (i >= A_X_G0) cnt = 32;
-            if (i == A_LOADED || i == A_DS_READY || i == A_DQ_FREE) cnt = 512;
+            if (i == A_LOADED || i == A_DQ_FREE) cnt = 512;
+            if (i >= A_DS_READY0 && i <= A_DS_READY3) cnt = 128;  // one per 32-key quarter of the step
             if (i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) cnt = 514;  // MMA warp (one lane), V producer, 512 row threads
             mbar_init(&bars[i], cnt);
         }
@@ -255,11 +257,16 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const SmemDesc desc_kmn = make_desc(smem_u32(sK), kQBox, 1024);  // K tile as MN-major operand of dQ
             uint32_t G = 0, items = 0;
             bool ok = true;
+            // The item's last step is the diagonal tile; at the ragged end of a sequence its K and V rows behind the end are
+            // set to zero (they meet dS = 0 and a masked dP only, but 0 * NaN is NaN): g_rag is that step, krows its rows
+            uint32_t g_rag = ~0u;
+            int krows = kStep;
             auto issue_s = [&](uint32_t g) {
                 const uint32_t kst = g % kDqKStages;
                 const SmemDesc dk = {desc_k.lo + kst * (kQBytes >> 4), desc_k.hi};
                 ok = mbar_wait(&bars[A_K_FULL0 + kst], (g / kDqKStages) & 1, abort_flag);
                 if (!ok) return;
+                if (g == g_rag) zero_rows_ool(sK + kst * kQBytes, kBoxes, kQBox, krows, kStep, lane);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
@@ -274,6 +281,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 const SmemDesc dv = {desc_v.lo + vst * (kQBytes >> 4), desc_v.hi};
                 ok = mbar_wait(&bars[A_V_FULL0 + vst], (g >> 1) & 1, abort_flag);
                 if (!ok) return;
+                if (g == g_rag) zero_rows_ool(sV + vst * kQBytes, kBoxes, kQBox, krows, kStep, lane);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
@@ -290,6 +298,8 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             Work wk;
             while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, wk, leader, true)) >= 0) {
                 const int n = wk.qt + 1;
+                krows = wk.len - wk.qt * kBM;
+                g_rag = krows < kStep ? G + n - 1 : ~0u;
                 ok = mbar_wait(&bars[A_QDO_FULL], items & 1, abort_flag);
                 if (!ok) break;
                 issue_s(G);
@@ -304,17 +314,23 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         issue_dp(g + 1, j + 2 == n);
                         if (!ok) break;
                     }
-                    ok = mbar_wait(&bars[A_DS_READY], g & 1, abort_flag);
-                    if (ok && j == 0) ok = mbar_wait(&bars[A_DQ_FREE], (items & 1) ^ 1, abort_flag);  // previous dQ read out
+                    if (j == 0) ok = mbar_wait(&bars[A_DQ_FREE], (items & 1) ^ 1, abort_flag);  // previous dQ read out
                     if (!ok) break;
-                    tc_fence_after();
                     const SmemDesc dkmn = {desc_kmn.lo + kst * (kQBytes >> 4), desc_kmn.hi};
                     const uint32_t a_ds = tmem + kColS + 128 * (g & 1);
+                    // dQ += dS K in slices of 32 keys, each as soon as that quarter's dS exists: the quarters finish one after
+                    // the other (leftmost first, the prefix chain), and the tensor pipe does not wait for the last one before
+                    // it starts on the first
 #pragma unroll
-                    for (int k = 0; k < kStep / 16; ++k) {
-                        if (k == 0) mma_ts_dyn(leader, tmem + kColDQ, a_ds, dkmn, 0, idesc_dq, j > 0);
-                        else mma_ts<true>(leader, tmem + kColDQ, a_ds + (k >> 1) * 32 + (k & 1) * 8, dkmn, k * 2048, idesc_dq);
+                    for (int qq = 0; qq < 4; ++qq) {
+                        ok = mbar_wait(&bars[A_DS_READY0 + qq], g & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (qq == 0) mma_ts_dyn(leader, tmem + kColDQ, a_ds, dkmn, 0, idesc_dq, j > 0);
+                        else mma_ts<true>(leader, tmem + kColDQ, a_ds + qq * 32, dkmn, 2 * qq * 2048, idesc_dq);
+                        mma_ts<true>(leader, tmem + kColDQ, a_ds + qq * 32 + 8, dkmn, (2 * qq + 1) * 2048, idesc_dq);
                     }
+                    if (!ok) break;
                     mma_commit(leader, &bars[A_K_EMPTY0 + kst]);
                     if (j + 2 < n) issue_s(g + 2);  // into the buffer whose dS the contraction above reads: in order
                 }
@@ -419,7 +435,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 // Every thread has begun this step once it has arrived at A_LOADED.  The wait keeps the row threads within one
                 // step of each other: the four warps of 32 rows exchange prefixes among themselves only, and without it one
                 // such quartet could finish the next step (dP of which is computed as soon as everybody has loaded this one)
-                // and complete this step's phase of A_DS_READY with its arrivals before another quartet has written its dS
+                // and complete this step's phase of its quarter's A_DS_READY with its arrivals before another quartet has written its dS
                 // (seen as garbage in dq of 32 rows, now and then).  It also keeps the exchange slots and barriers safe across
                 // items.  Barriers by step parity, so that a waiter is never two phases away from the phase it names.
                 ok = mbar_wait(&bars[A_LOADED], g & 1, abort_flag);
@@ -449,7 +465,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_st16(lane_base + kColS + 128 * buf + 32 * kq, packed);
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(&bars[A_DS_READY]);
+                mbar_arrive(&bars[A_DS_READY0 + kq]);
                 if (kDefer && j == 0 && have_pend) {
                     store_item();
                     if (!ok) break;
@@ -721,9 +737,29 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const SmemDesc desc_qmn = make_desc(smem_u32(sQl), kKBox, 1024), desc_domn = make_desc(smem_u32(sDOl), kKBox, 1024);  // MN-major
             const SmemDesc desc_p = make_desc(smem_u32(sP), kKBox, 1024), desc_ds = make_desc(smem_u32(sDS), kKBox, 1024);
             bool ok = true;
-            auto issue_sdp = [&](uint32_t g, bool last_of_item) {
+            // Ragged ends.  The rows of a tile behind the end of its sequence belong to the next sequence or to nobody; they
+            // meet zero weights only, but a zero weight does not silence a NaN.  K, V of the sequence's last key tile: the
+            // rows behind the end are set to zero.  Q, dO of its last query tile, which is the last step of every item:
+            // dk, dv contract over query rows in slices of 16, so the slices that lie behind the end are not issued at all,
+            // and only the rows between the end and the next multiple of 16 are set to zero, in all four copies of the
+            // tile (with Q and dO zero, S and dP of such a row are zero, and so are its p and ds).
+            const auto zero_kv = [&](const KvWork& e) {
+                const int krows = e.len - e.kt * kKT;
+                if (krows < kKT) {
+                    zero_rows(sK, kBoxes, kQBox, krows, kKT, lane);
+                    zero_rows(sV, kBoxes, kQBox, krows, kKT, lane);
+                    zero_rows_done();
+                }
+            };
+            const auto last_rows = [](const KvWork& e) { return e.len - (e.n_qt - 1) * kBM; };  // 1 ... 128
+            auto issue_sdp = [&](uint32_t g, bool last_of_item, int qrows) {
                 ok = mbar_wait(&bars[B_E_FULL], g & 1, abort_flag);
                 if (!ok) return;
+                if (last_of_item && (qrows & 15)) {
+                    zero_rows_to_16(sQe, kBoxes, kQBox, qrows, lane);
+                    zero_rows_to_16(sDOe, kBoxes, kQBox, qrows, lane);
+                    zero_rows_done();
+                }
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
@@ -751,34 +787,51 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             bool have = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, wk, leader, true) >= 0;
             if (have) {
                 ok = mbar_wait(&bars[B_KV_FULL], 0, abort_flag);
-                if (ok) issue_sdp(0, wk.n_qt - wk.kt == 1);
+                if (ok) {
+                    zero_kv(wk);
+                    issue_sdp(0, wk.n_qt - wk.kt == 1, last_rows(wk));
+                }
             }
             while (ok && have) {
                 const int n = wk.n_qt - wk.kt;
+                const int qrows = last_rows(wk);
                 for (int j = 0; ok && j < n; ++j, ++g) {
+                    const int rows = j + 1 == n ? qrows : kBM;  // query rows of this step that belong to the sequence
                     if (j + 1 < n) {
                         ok = mbar_wait(&bars[B_LOADED], g & 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
-                        issue_sdp(g + 1, j + 2 == n);
+                        issue_sdp(g + 1, j + 2 == n, qrows);
                     } else {  // the next item is fetched here, off the path between two items
                         have = sched.next(ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, nx, leader, true) >= 0;
                     }
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {  // 32 query rows at a time: region i & 1 of the p / ds buffers
                         const int hh = i >> 1, b = i & 1;
+                        if (b == 0) {
+                            ok = mbar_wait(&bars[B_L_FULL0 + hh], g & 1, abort_flag);
+                            if (!ok) break;
+                            // the slice of 16 rows that straddles the end, in its 64-row half: here, while the row threads
+                            // are still at work on the region's p and ds, and not when the contractions are due
+                            if ((rows & 15) && (rows >> 6) == hh) {
+                                zero_rows_to_16(sQl + hh * kHalfBytes, kBoxes, kKBox, rows & 63, lane);
+                                zero_rows_to_16(sDOl + hh * kHalfBytes, kBoxes, kKBox, rows & 63, lane);
+                                zero_rows_done();
+                            }
+                        }
                         ok = mbar_wait(&bars[B_PDS_READY0 + b], hh, abort_flag);  // a region is used twice per step
-                        if (ok && b == 0) ok = mbar_wait(&bars[B_L_FULL0 + hh], g & 1, abort_flag);
                         if (ok && j == 0 && i == 0)  // the previous item's accumulators must have been read out
                             ok = mbar_wait(&bars[B_DKV_FREE], (items & 1) ^ 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
                         const SmemDesc ddo = {desc_domn.lo + hh * (kHalfBytes >> 4), desc_domn.hi};
                         const SmemDesc dq = {desc_qmn.lo + hh * (kHalfBytes >> 4), desc_qmn.hi};
-                        mma_ss_dyn(leader, tmem + kColDV, desc_p, b * 4096, ddo, b * 4096, idesc_t, j > 0 || i > 0);
-                        mma_ss<true>(leader, tmem + kColDV, desc_p, b * 4096 + 2048, ddo, b * 4096 + 2048, idesc_t);
-                        mma_ss_dyn(leader, tmem + kColDK, desc_ds, b * 4096, dq, b * 4096, idesc_t, j > 0 || i > 0);
-                        mma_ss<true>(leader, tmem + kColDK, desc_ds, b * 4096 + 2048, dq, b * 4096 + 2048, idesc_t);
+                        if (32 * i < rows) {  // slices of 16 query rows that lie behind the end of the sequence are left out
+                            mma_ss_dyn(leader, tmem + kColDV, desc_p, b * 4096, ddo, b * 4096, idesc_t, j > 0 || i > 0);
+                            if (32 * i + 16 < rows) mma_ss<true>(leader, tmem + kColDV, desc_p, b * 4096 + 2048, ddo, b * 4096 + 2048, idesc_t);
+                            mma_ss_dyn(leader, tmem + kColDK, desc_ds, b * 4096, dq, b * 4096, idesc_t, j > 0 || i > 0);
+                            if (32 * i + 16 < rows) mma_ss<true>(leader, tmem + kColDK, desc_ds, b * 4096 + 2048, dq, b * 4096 + 2048, idesc_t);
+                        }
                         mma_commit(leader, &bars[B_PDS_FREE0 + 2 * b + hh]);
                         if (b == 1) mma_commit(leader, &bars[B_L_EMPTY0 + hh]);
                     }
@@ -790,8 +843,9 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (have) {
                     ok = mbar_wait(&bars[B_LOADED], (g - 1) & 1, abort_flag) && mbar_wait(&bars[B_KV_FULL], items & 1, abort_flag);
                     if (!ok) break;
+                    zero_kv(wk);
                     tc_fence_after();
-                    issue_sdp(g, wk.n_qt - wk.kt == 1);
+                    issue_sdp(g, wk.n_qt - wk.kt == 1, last_rows(wk));
                 }
             }
         }

@@ -264,10 +264,20 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     ok = mbar_wait(&bars[V_FULL0 + st], ph_vf, abort_flag);
                     ph_vf ^= 1;
                     if (!ok) break;
+                    int vrows = kBN;  // keys of the step's tile that belong to the sequence
                     if (j == 0) {  // the previous item's O must have been read out
                         ok = mbar_wait(&bars[O_FREE], ph_of, abort_flag);
                         ph_of ^= 1;
                         if (!ok) break;
+                        // Diagonal tile at the ragged end of a sequence: the V rows behind the end belong to the next sequence
+                        // or to nobody.  They meet P = 0 only, but a zero weight does not silence a NaN: the slices of 16
+                        // keys that lie behind the end are not issued, and the rows between the end and the next multiple of
+                        // 16 are set to zero.
+                        vrows = wk.len - wk.qt * kBM;
+                        if (vrows < kBN && (vrows & 15)) {
+                            zero_rows_to_16(sV + st * kTileBytes, kBoxes, kBoxBytes, vrows, lane);
+                            zero_rows_done();
+                        }
                     }
                     tc_fence_after();
                     const SmemDesc dv = {desc_v.lo + st * (kTileBytes >> 4), desc_v.hi};
@@ -275,7 +285,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
                     for (int k = 0; k < kBN / 16; ++k) {
                         if (k == 0) mma_ts_dyn(leader, tmem + kColO, a_p, dv, 0, idesc_o, j > 0);
-                        else mma_ts<true>(leader, tmem + kColO, a_p + k * 8, dv, k * 2048, idesc_o);
+                        else if (16 * k < vrows) mma_ts<true>(leader, tmem + kColO, a_p + k * 8, dv, k * 2048, idesc_o);
                     }
                     mma_commit(leader, &bars[V_EMPTY0 + st]);
                     if (j + 3 < n) issue_s(j + 3, n);

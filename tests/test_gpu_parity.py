@@ -321,6 +321,32 @@ def test_recomputed_carries_give_the_same_gradients():
         assert np.array_equal(x, y)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("path", ["tensor", "simt"])
+def test_non_finite_rows_outside_a_sequence_do_not_leak(path, D):
+    """NaN in the rows behind the ragged end of a sequence (the pad behind the last sequence; a neighbouring sequence) must
+    not reach the sequence's results: the kernels load whole 128-row tiles, and a zero weight does not silence a NaN.
+    Sequences of three and two tiles, so that off-diagonal steps see the ragged query tile too."""
+    import stickbreaking_attention_b200 as sb
+    lengths = [300, 200]
+    H, T = 2, 640
+    ends = np.cumsum(lengths)
+    for poisoned in ("pad", "neighbour"):
+        ins = [rounded(x, torch.bfloat16) for x in synth(H, T, D, seed=41)]
+        lo, hi = (ends[1], T) if poisoned == "pad" else (ends[0], T)
+        clean = [x[:, :lo].copy() for x in ins]
+        for x in ins:
+            x[:, lo:hi] = np.nan
+        sb.set_path(path)
+        try:
+            got = run_varlen(*ins, lengths, 0.1, False, torch.bfloat16)
+        finally:
+            sb.set_path("auto")
+        kept = lengths if poisoned == "pad" else lengths[:1]
+        want = oracle_varlen(*clean, kept, 0.1, False)
+        assert_close(NAMES, [x[:, :lo] for x in got], want, TOL_BF16, f"NaN in the {poisoned}, {path} path, D={D}")
+
+
 def test_empty_and_no_grad():
     from stickbreaking_attention_b200 import sb_attn_varlen
     q = torch.randn(2, 0, 64, device="cuda", dtype=torch.bfloat16)
