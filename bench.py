@@ -623,8 +623,8 @@ def run_ours(args, wl):
                 "kernel_ms": kernels,
                 "kernel_tflops": {kk: fl_rank * share[kk] / (vv * 1e-3) / 1e12 for kk, vv in kernels.items()},
             }
-        cpu = None
-        if "cpu" not in skip:
+        cpu = None  # timed at N = 1 only: with more ranks the other processes' polling threads share the host cores
+        if "cpu" not in skip and world == 1:
             threads = cpu_threads()
             cpu_seqs = cpu_sample_of(wl)
             cpu_reference_step(wl, cpu_seqs[:1])

@@ -1,6 +1,6 @@
 // fp32-arithmetic kernels (no tensor cores): forward, backward-dq and backward-dk/dv.
 //
-// They serve float32 inputs (where products must not be rounded to bf16/tf32), head dims that are not 64 or
+// They serve float32 inputs (where products must not be rounded to bf16/tf32), head dims other than 32, 64 and
 // 128, and tensors whose strides the TMA path cannot take.  Structure mirrors the tensor-core kernels:
 //   * forward walks the key tiles of one 64-row query block right to left and carries, per row, the running
 //     product W = prod(1 - beta) of everything to the right (the reference carries its log,
