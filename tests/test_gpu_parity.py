@@ -321,19 +321,20 @@ def test_recomputed_carries_give_the_same_gradients():
         assert np.array_equal(x, y)
 
 
-@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("lengths", [[300, 200], [272, 129, 255]])
+@pytest.mark.parametrize("D", [32, 64, 128])
 @pytest.mark.parametrize("path", ["tensor", "simt"])
-def test_non_finite_rows_outside_a_sequence_do_not_leak(path, D):
-    """NaN in the rows behind the ragged end of a sequence (the pad behind the last sequence; a neighbouring sequence) must
-    not reach the sequence's results: the kernels load whole 128-row tiles, and a zero weight does not silence a NaN.
-    Sequences of three and two tiles, so that off-diagonal steps see the ragged query tile too."""
+def test_non_finite_rows_outside_a_sequence_do_not_leak(path, D, lengths):
+    """NaN in the rows behind the ragged end of a sequence (the pad behind the last sequence; the sequences that follow)
+    must not reach the sequence's results: the kernels load whole 128-row tiles, and a zero weight does not silence a
+    NaN.  Sequences of two and three tiles, so that off-diagonal steps see the ragged query tile too; ends in either
+    64-row half of a tile, on a multiple of 16 rows, one row into a tile and one row short of one."""
     import stickbreaking_attention_b200 as sb
-    lengths = [300, 200]
-    H, T = 2, 640
+    H, T = 2, 768
     ends = np.cumsum(lengths)
     for poisoned in ("pad", "neighbour"):
         ins = [rounded(x, torch.bfloat16) for x in synth(H, T, D, seed=41)]
-        lo, hi = (ends[1], T) if poisoned == "pad" else (ends[0], T)
+        lo, hi = (ends[-1], T) if poisoned == "pad" else (ends[0], T)
         clean = [x[:, :lo].copy() for x in ins]
         for x in ins:
             x[:, lo:hi] = np.nan
