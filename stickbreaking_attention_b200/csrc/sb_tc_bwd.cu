@@ -206,7 +206,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             Work wk;
             const auto fetch = [&](int w_) { return fetch_work(a, n_items, w_); };
             while (ok && (w = sched.next(a.sched + 2, n_work, ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, fetch, wk)) >= 0) {
-                ok = mbar_wait(&bars[A_QDO_EMPTY], (items & 1) ^ 1, abort_flag);
+                ok = mbar_wait_idle(&bars[A_QDO_EMPTY], (items & 1) ^ 1, abort_flag);
                 ++items;
                 if (!ok) break;
                 mbar_expect_tx(&bars[A_QDO_FULL], 2 * kQBytes);
@@ -217,7 +217,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
                 for (int j = 0; j <= wk.qt; ++j, ++G) {
                     const uint32_t st = G % kDqKStages;
-                    ok = mbar_wait(&bars[A_K_EMPTY0 + st], ((G / kDqKStages) & 1) ^ 1, abort_flag);
+                    ok = mbar_wait_idle(&bars[A_K_EMPTY0 + st], ((G / kDqKStages) & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(&bars[A_K_FULL0 + st], kQBytes);
 #pragma unroll
@@ -237,7 +237,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             while (ok && (w = sched.next(ring, &bars[A_WORK_FULL0], &bars[A_WORK_EMPTY0], abort_flag, wk)) >= 0) {
                 for (int j = 0; j <= wk.qt; ++j, ++G) {
                     const uint32_t st = G & 1;
-                    ok = mbar_wait(&bars[A_V_EMPTY0 + st], ((G >> 1) & 1) ^ 1, abort_flag);
+                    ok = mbar_wait_idle(&bars[A_V_EMPTY0 + st], ((G >> 1) & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(&bars[A_V_FULL0 + st], kQBytes);
 #pragma unroll
@@ -679,7 +679,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             KvWork wk;
             const auto fetch = [&](int w_) { return fetch_kv_work(a, n_items, w_); };
             while (ok && (w = sched.next(a.sched + 4, n_work, ring, &bars[B_WORK_FULL0], &bars[B_WORK_EMPTY0], abort_flag, fetch, wk)) >= 0) {
-                ok = mbar_wait(&bars[B_KV_EMPTY], (items & 1) ^ 1, abort_flag);
+                ok = mbar_wait_idle(&bars[B_KV_EMPTY], (items & 1) ^ 1, abort_flag);
                 ++items;
                 if (!ok) break;
                 mbar_expect_tx(&bars[B_KV_FULL], 2 * kQBytes);
@@ -689,7 +689,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tma_load_4d(sV + bx * kQBox, &map_v, &bars[B_KV_FULL], bx * 64, wk.start + wk.kt * kKT, wk.h, wk.b);
                 }
                 for (int i = wk.kt; i < wk.n_qt; ++i, ++G) {
-                    ok = mbar_wait(&bars[B_E_EMPTY], (G & 1) ^ 1, abort_flag);
+                    ok = mbar_wait_idle(&bars[B_E_EMPTY], (G & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(&bars[B_E_FULL], 2 * kQBytes);
 #pragma unroll
@@ -712,7 +712,7 @@ tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 for (int i = wk.kt; ok && i < wk.n_qt; ++i, ++G) {
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
-                        ok = mbar_wait(&bars[B_L_EMPTY0 + hh], (G & 1) ^ 1, abort_flag);
+                        ok = mbar_wait_idle(&bars[B_L_EMPTY0 + hh], (G & 1) ^ 1, abort_flag);
                         if (!ok) break;
                         mbar_expect_tx(&bars[B_L_FULL0 + hh], kQBytes);
 #pragma unroll

@@ -161,7 +161,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             Work wk;
             const auto fetch = [&](int w_) { return fetch_work(a, n_items, w_); };
             while (ok && (w = sched.next(a.sched + 0, n_work, ring, &bars[WORK_FULL0], &bars[WORK_EMPTY0], abort_flag, fetch, wk)) >= 0) {
-                ok = mbar_wait(&bars[Q_EMPTY], ph_qe, abort_flag);
+                ok = mbar_wait_idle(&bars[Q_EMPTY], ph_qe, abort_flag);
                 ph_qe ^= 1;
                 if (!ok) break;
                 mbar_expect_tx(&bars[Q_FULL], kTileBytes);
@@ -169,7 +169,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 for (int bx = 0; bx < kBoxes; ++bx)
                     tma_load_4d(sQ + bx * kBoxBytes, &map_q, &bars[Q_FULL], bx * 64, wk.start + wk.qt * kBM, wk.h, wk.b);
                 for (int kt = wk.qt; kt >= 0; --kt) {
-                    ok = mbar_wait(&bars[K_EMPTY0 + st], (ph_ke >> st) & 1, abort_flag);
+                    ok = mbar_wait_idle(&bars[K_EMPTY0 + st], (ph_ke >> st) & 1, abort_flag);
                     ph_ke ^= 1u << st;
                     if (!ok) break;
                     mbar_expect_tx(&bars[K_FULL0 + st], kTileBytes);
@@ -194,7 +194,7 @@ tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 for (int kt = wk.qt; kt >= 0; --kt, ++kv) {
                     const int st = kv & 1;
                     uint32_t& ph_ve = st ? ph_ve1 : ph_ve0;
-                    ok = mbar_wait(&bars[V_EMPTY0 + st], ph_ve, abort_flag);
+                    ok = mbar_wait_idle(&bars[V_EMPTY0 + st], ph_ve, abort_flag);
                     ph_ve ^= 1;
                     if (!ok) break;
                     mbar_expect_tx(&bars[V_FULL0 + st], kTileBytes);
