@@ -54,6 +54,24 @@ def test_varlen_fused_against_oracle(D, dtype, attend_current):
     assert_close(NAMES, [x.double().cpu().numpy() for x in got], want, TOL_BF16, f"fused packed D={D}")
 
 
+def test_varlen_fused_ignores_nan_behind_the_last_sequence():
+    """The fused kernels with NaN in the pad behind the last sequence (the epilogues read v and dO rows themselves)."""
+    from stickbreaking_attention_b200 import check_status, sb_attn_varlen
+    lengths = [300, 200]
+    H, T, D, used = 2, 640, 128, 500
+    ins = [rounded(x, torch.bfloat16) for x in synth(H, T, D, 23)]
+    clean = [x[:, :used].copy() for x in ins]
+    for x in ins:
+        x[:, used:] = np.nan
+    q, k, v, dout, dr = (torch.from_numpy(x).to("cuda", torch.bfloat16) for x in ins)
+    cu = torch.tensor(np.cumsum(lengths), dtype=torch.int64, device="cuda")
+    got = _run(lambda q, k, v: sb_attn_varlen(q, k, v, cu, max(lengths), inv_temp=0.1, zero_start=False, fuse_remainder=True),
+               q, k, v, dout, dr)
+    check_status()
+    want = _oracle_fused(*clean, lengths, 0.1, False)
+    assert_close(NAMES, [x.double().cpu().numpy()[:, :used] for x in got], want, TOL_BF16, "fused packed, NaN pad")
+
+
 def test_batched_fused_against_oracle():
     from stickbreaking_attention_b200 import check_status, sb_attn
     B, H, T, D = 2, 2, 300, 128
