@@ -170,7 +170,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             uint32_t cnt = 1;
             if (i >= A_X_G0) cnt = 32;
             if (i == A_LOADED || i == A_DQ_FREE) cnt = 512;
-            if (i >= A_DS_READY0 && i <= A_DS_READY3) cnt = 128;  // one per 32-key quarter of the step
+            if (i >= A_DS_READY0 && i <= A_DS_READY3) cnt = kDefer ? 512 : 128;  // one per 32-key quarter of the step, or one for all
             if (i == A_WORK_EMPTY0 || i == A_WORK_EMPTY1) cnt = 514;  // MMA warp (one lane), V producer, 512 row threads
             mbar_init(&bars[i], cnt);
         }
@@ -321,11 +321,15 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     // dQ += dS K in slices of 32 keys, each as soon as that quarter's dS exists: the quarters finish one after
                     // the other (leftmost first, the prefix chain), and the tensor pipe does not wait for the last one before
                     // it starts on the first
+                    // (-1.5 % on long sequences; on packs of short ones, the kDefer instantiation, one barrier for all four
+                    // quarters is 3 % faster)
 #pragma unroll
                     for (int qq = 0; qq < 4; ++qq) {
-                        ok = mbar_wait(&bars[A_DS_READY0 + qq], g & 1, abort_flag);
-                        if (!ok) break;
-                        tc_fence_after();
+                        if (!kDefer || qq == 0) {
+                            ok = mbar_wait(&bars[A_DS_READY0 + qq], g & 1, abort_flag);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
                         if (qq == 0) mma_ts_dyn(leader, tmem + kColDQ, a_ds, dkmn, 0, idesc_dq, j > 0);
                         else mma_ts<true>(leader, tmem + kColDQ, a_ds + qq * 32, dkmn, 2 * qq * 2048, idesc_dq);
                         mma_ts<true>(leader, tmem + kColDQ, a_ds + qq * 32 + 8, dkmn, (2 * qq + 1) * 2048, idesc_dq);
@@ -465,7 +469,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_st16(lane_base + kColS + 128 * buf + 32 * kq, packed);
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(&bars[A_DS_READY0 + kq]);
+                mbar_arrive(&bars[A_DS_READY0 + (kDefer ? 0 : kq)]);
                 if (kDefer && j == 0 && have_pend) {
                     store_item();
                     if (!ok) break;
