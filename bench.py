@@ -2,7 +2,7 @@
 """Benchmark of stick-breaking attention forward+backward (packed variable-length layout, bf16).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
-                    [--heads H] [--skip kernels,e2e,cpu,sustained,c5,short]
+                    [--heads H] [--skip kernels,e2e,cpu,sustained,c5,short,graph]
 
 One step = one forward and one backward over one synthetic batch through the public API (``sb_attn_varlen`` +
 autograd).  Prints ONE JSON line on rank 0.
@@ -415,6 +415,23 @@ def run_ours(args, wl):
     launches_per_step = launch_count() - n0  # kernels the library launched, counted inside the library
     ms_step, win_main = timed(step, args.steps, max(args.warmup, 3))
 
+    # ---------------------------------------------------------------- the same step replayed from a CUDA graph
+    # (the launch-bound workloads only: the launchers enqueue kernels on the caller's stream and nothing else, so forward and
+    # backward replay from one graph launch without the Python layer and the per-kernel launch cost)
+    graph_rec = None
+    if "graph" not in skip and rank == 0 and world == 1 and wl["name"].split("-")[0] in ("c1", "b500"):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            step()
+        ms_graph, _ = timed(cg.replay, args.steps, max(args.warmup, 3))
+        graph_rec = {"ms_per_step": ms_graph, "eager_ms_per_step": ms_step,
+                     "what": "forward + backward captured once with torch.cuda.graph, one replay per step"}
+
     # ---------------------------------------------------------------- per-kernel times, events on the launching stream
     def time_kernel(fn, reps):
         fn()
@@ -647,7 +664,7 @@ def run_ours(args, wl):
                 peaks["bf16_tflops"], peaks["source"]),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
-            "clocks": clocks, "sustained": sustained, "short": short, "c5_strong": c5,
+            "clocks": clocks, "sustained": sustained, "short": short, "c5_strong": c5, "graph_replay": graph_rec,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -663,7 +680,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "short", "c1", "b500"])
     ap.add_argument("--heads", type=int, default=0, help="run a subset of the workload's heads (profiling runs)")
-    ap.add_argument("--skip", default="", help="comma list of parts to leave out: kernels,e2e,cpu,sustained,c5,short")
+    ap.add_argument("--skip", default="", help="comma list of parts to leave out: kernels,e2e,cpu,sustained,c5,short,graph")
     args = ap.parse_args()
     args.skip = set(x for x in args.skip.split(",") if x)
     wl = workload(args.workload)
