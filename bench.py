@@ -452,11 +452,25 @@ def run_ours(args, wl):
             outs = (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v))
             _, bwd_bytes = ops._workspace_sizes(ops._base_params(q, False, cu, max_len, it, False, True))
             bws = torch.empty(bwd_bytes, dtype=torch.uint8, device=dev)
-            kernels["fwd"] = time_kernel(lambda: ops.varlen_fwd(q, k, v, cu, max_len, it), reps)
-            kernels["bwd_dq"] = time_kernel(
-                lambda: ops.varlen_bwd(do, drem, q, k, v, cu, max_len, ws, it, phases=1, out=outs, bwd_workspace=bws), reps)
-            kernels["bwd_dkdv"] = time_kernel(
-                lambda: ops.varlen_bwd(do, drem, q, k, v, cu, max_len, ws, it, phases=2, out=outs, bwd_workspace=bws), reps)
+            # the three launchers in the order of a step, an event between them: every kernel is timed under the conditions
+            # of the step (clocks, power state, cache contents), and the three times add up to it
+            calls = (("fwd", lambda: ops.varlen_fwd(q, k, v, cu, max_len, it)),
+                     ("bwd_dq", lambda: ops.varlen_bwd(do, drem, q, k, v, cu, max_len, ws, it, phases=1, out=outs,
+                                                       bwd_workspace=bws)),
+                     ("bwd_dkdv", lambda: ops.varlen_bwd(do, drem, q, k, v, cu, max_len, ws, it, phases=2, out=outs,
+                                                         bwd_workspace=bws)))
+            for _, fn in calls:
+                fn()
+            evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(reps)]
+            torch.cuda.synchronize()
+            for ev in evs:
+                ev[0].record()
+                for i, (_, fn) in enumerate(calls):
+                    fn()
+                    ev[i + 1].record()
+            torch.cuda.synchronize()
+            for i, (name, _) in enumerate(calls):
+                kernels[name] = sum(ev[i].elapsed_time(ev[i + 1]) for ev in evs) / reps
             del o_, rem_, nla_, ws, outs, bws
 
     # ---------------------------------------------------------------- sustained: the same step for at least two seconds
