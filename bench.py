@@ -18,6 +18,9 @@ line carries three further records, each timed the same way (CUDA events, max ov
   sustained  the default step repeated for at least two seconds, with the SM clock sampled meanwhile
   short      a pack of 128-token sequences (memory-bound): achieved HBM GB/s against the measured copy bandwidth
 
+and, for the two small workloads c1 and b500, ``graph_replay``: the step captured once into a CUDA graph and replayed.
+``cpu_baseline`` (the reference's sb_ref.py on the host cores, a bounded sample) is timed at N = 1 only.
+
 Workloads (seeded synthetic data, N(0,1) inputs rounded to bf16, inv_temp = 1/sqrt(D)):
   c2     32 heads, head_dim 128, 16384 tokens packed from lengths drawn uniformly in [256, 4096]  (default)
   c3     32 heads, head_dim 128, 8 sequences of 4096 tokens
