@@ -68,7 +68,7 @@ __device__ __forceinline__ void stick4(float s0, float s1, float s2, float s3, f
 }
 
 // ================================================================================================ dq kernel
-// One block per SM (608 threads, at most 104 registers each), one work item = (head, sequence, 128-row query tile) at a
+// One block per SM (608 threads: 19 warps put five on one scheduler, which caps a thread at 96 registers), one work item = (head, sequence, 128-row query tile) at a
 // time, walked LEFT TO RIGHT in steps of 128 keys, so that every contraction runs at the widest shape: S and dP
 // [128 q x 128 keys], dQ += dS K with K = 128 (an MMA instruction costs the same for N = 64 and N = 128; 64-key steps need
 // 40 instructions per 128 x 128 scores, 128-key steps 24).
@@ -492,7 +492,7 @@ tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 // ================================================================================================ dk/dv kernel
-// One block per SM (608 threads, at most 104 registers each) keeps a 128-key tile stationary and walks the 128-row query
+// One block per SM (608 threads: 19 warps put five on one scheduler, which caps a thread at 96 registers) keeps a 128-key tile stationary and walks the 128-row query
 // tiles below it.  All four contractions run with M = 128 and N = 128 (N = D for the last two), the widest shape that 512
 // columns of tensor memory allow: S and dP [128 q x 128 keys], dv and dk [128 keys x D] (an MMA instruction costs the same
 // ~65 cycles for N = 64 and N = 128, so narrow tiles waste half of the tensor pipe).  Tensor memory is full with these

@@ -7,7 +7,7 @@
 // (stickbreaking_attention/sb_varlen/sb_varlen_fwd.py:155-193) -- because the weight of key j needs the product of
 // (1 - beta) over the keys to its right.
 //
-// Warps of a block (608 threads, at most 104 registers each):
+// Warps of a block (608 threads: 19 warps put five on one scheduler, which caps a thread at 96 registers):
 //   0-15       row warps: a thread owns one query row and a quarter (32 keys) of every tile, warps 0-3 the rightmost
 //              quarter ... warps 12-15 the leftmost, so that every scheduler has four row warps to choose from.
 //              S lives in three rotating buffers in tensor memory, so the tensor cores are always two tiles ahead:
