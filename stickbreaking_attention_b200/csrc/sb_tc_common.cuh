@@ -71,6 +71,39 @@ __device__ __forceinline__ void store_row32(char* dst, const uint32_t (&v)[32], 
     }
 }
 
+// The same for the two rows of a lane pair at once.  Lanes l and l ^ 1 own consecutive rows; after one exchange the even
+// lane holds the first 32 bytes of both rows' 64 and the odd lane the second 32, so that the 64 bytes of a row leave in one
+// instruction from two neighbouring lanes: 16 instead of 32 distinct lines per store instruction, and a 128 x 128 tile
+// leaves the SM in ~1 100 instead of ~2 000 cycles (measured in isolation).  `dst` is this lane's own row, `row_bytes` the
+// distance between consecutive rows, `ok` whether this lane's row is to be written.  All 32 lanes must call.
+template <bool kF16>
+__device__ __forceinline__ void store_row32_pairs(char* dst, const uint32_t (&v)[32], float sc, int64_t row_bytes, bool ok, int lane) {
+    uint32_t u[16], s[8];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) u[j] = pack16<kF16>(__uint_as_float(v[2 * j]) * sc, __uint_as_float(v[2 * j + 1]) * sc);
+    const bool hi = lane & 1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] = __shfl_xor_sync(0xffffffffu, hi ? u[j] : u[8 + j], 1);  // the half the partner writes
+    const bool ok_other = __shfl_xor_sync(0xffffffffu, (int)ok, 1) != 0;
+    char* own = dst + (hi ? 32 : 0);
+    char* oth = own + (hi ? -row_bytes : row_bytes);
+    const auto put = [](char* p, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t a4, uint32_t a5, uint32_t a6, uint32_t a7) {
+        if ((reinterpret_cast<uintptr_t>(p) & 31) == 0) {
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(a4),
+                         "r"(a5), "r"(a6), "r"(a7)
+                         : "memory");
+        } else {
+            *(uint4*)p = make_uint4(a0, a1, a2, a3);
+            *(uint4*)(p + 16) = make_uint4(a4, a5, a6, a7);
+        }
+    };
+    if (ok) {
+        if (hi) put(own, u[8], u[9], u[10], u[11], u[12], u[13], u[14], u[15]);
+        else put(own, u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
+    }
+    if (ok_other) put(oth, s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7]);
+}
+
 // 32 16-bit values at `src` as fp32
 template <bool kF16>
 __device__ __forceinline__ void load_row32(const char* src, float (&x)[32]) {
